@@ -1,0 +1,154 @@
+/*
+ * sphconv_b200 - C ABI of the B200 (sm_100a) implementation of the sphconv hot path:
+ * rule (input/output index pair) generation over the range-voxel format and the
+ * rule-driven sparse convolution (forward, dgrad, wgrad).
+ *
+ * Conventions
+ *  - Every pointer named d_* or documented "device" is a CUDA device pointer on the current device.
+ *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises
+ *    unless stated.
+ *  - Every function returns SPH_OK (0) or a negative SPH_ERR_* code and never exits the process.
+ *    sph_last_error() returns a human readable message for the calling thread.
+ *  - No function allocates device memory; scratch is caller-provided and sized by the
+ *    *_scratch_bytes helpers.
+ *  - Range-voxel format (reference: sphconv/tensor.py:33-125, src/sphconv/tensor.cu:107-109):
+ *    z_ptr int32 [B,H,W] is an INCLUSIVE prefix sum over (b,h,w) row-major, global over the batch;
+ *    column c (flat index) owns feature rows [c ? z_ptr[c-1] : 0, z_ptr[c]); z_idx int32 [NNZ] holds the
+ *    depth index of every row.  in_shape/out_shape are {H, W, D} with D the compressed axis.
+ *
+ * Citations "ref:" give the file:line of reveriel/sphconv that the entry point replaces.
+ */
+#ifndef SPHCONV_B200_H_
+#define SPHCONV_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPH_OK 0
+#define SPH_ERR_INVALID (-1)     /* bad argument (null pointer, non-positive size, inconsistent shapes) */
+#define SPH_ERR_UNSUPPORTED (-2) /* valid request this build does not implement (e.g. dilation != 1) */
+#define SPH_ERR_CUDA (-3)        /* a CUDA runtime call failed; see sph_last_error() */
+#define SPH_ERR_LIMIT (-4)       /* size beyond a documented maximum */
+
+/* bits of the device status word the kernels OR into (*d_status); 0 means clean */
+#define SPH_STATUS_RULE_OVERFLOW 1 /* a (tile,k) list exceeded tile_n_max; extra pairs were not stored */
+#define SPH_STATUS_BAD_INDEX 2     /* a z index / row id outside its valid range was met and skipped */
+#define SPH_STATUS_TIMEOUT 4       /* a bounded device-side wait ran out */
+
+enum sph_dtype { SPH_F32 = 0, SPH_F16 = 1, SPH_BF16 = 2, SPH_I8 = 3 };
+
+/* Geometry of one convolution layer.  ref: argument list of get_rules / get_rules_subm,
+ * include/sphconv/rules.h:8-32 (batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize). */
+typedef struct sph_geom {
+  int32_t B;
+  int32_t in_shape[3];  /* H, W, D */
+  int32_t out_shape[3]; /* oH, oW, oD */
+  int32_t ksize[3];
+  int32_t stride[3];
+  int32_t padding[3];
+  int32_t tile[2]; /* output tile (tH, tW); default of the reference is {2,2}, sphconv/conv.py:105 */
+} sph_geom;
+
+const char* sph_last_error(void);
+int sph_version(void);
+
+/* ---- host-side geometry helpers --------------------------------------------------------------- */
+
+/* ref: out_spatial, sphconv/utils/__init__.py:27-44 (dilation fixed to 1). */
+int sph_out_spatial(const int32_t in_shape[3], const int32_t ksize[3], const int32_t stride[3],
+                    const int32_t padding[3], int32_t out_shape[3]);
+
+/* ref: huristic_tile_n_max + getInTileSize, src/sphconv/rules.cu:21-34; bit-identical result. */
+int sph_tile_n_max(const sph_geom* g, int64_t nnz);
+
+/* Number of tiles, ref: src/sphconv/rules.cu:353 and get_tile_grid_shape, sphconv/conv.py:32-38. */
+int sph_num_tiles(const sph_geom* g);
+
+/* ---- rule generation -------------------------------------------------------------------------- */
+
+/* Submanifold rules.  ref: get_rules_subm, src/sphconv/rules.cu:326-390.
+ *   d_rules      int32 [NTile, KV, 2, tile_n_max]  (may be null: only the neighbour tables are produced)
+ *   d_rule_size  int32 [NTile, KV]                  (may be null together with d_rules)
+ *   d_nbr        int32 [KV, nnz]: d_nbr[k][o] = input row paired with output row o at offset k, or -1 (may be null)
+ *   fill_unused  != 0: entries of d_rules past rule_size are set to -1 as the reference does (rules.cu:364-366)
+ * The pair multiset of every (tile,k) list equals the reference's; the order inside a list is unspecified
+ * there (atomics) and deterministic here. */
+int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
+                   int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int32_t* d_nbr,
+                   int fill_unused, int32_t* d_status, void* stream);
+
+/* Strided ("regular") sparse conv, step 1: output sparsity pattern.
+ * ref: get_rules, src/sphconv/rules.cu:405-462 (prepareGridKernel + the cumsum/roll scans).
+ *   d_scratch   sph_rules_strided_scratch_bytes(g) bytes; must be kept untouched until step 2 has run
+ *   d_oz_ptr    int32 [B,oH,oW], inclusive prefix like z_ptr
+ *   d_out_nnz   int32 [1] on the device (= oz_ptr[-1])
+ *   h_out_nnz   optional host pointer: when non-null the call synchronises `stream` and stores the
+ *               count there (the same device->host read the reference does at rules.cu:461) */
+int64_t sph_rules_strided_scratch_bytes(const sph_geom* g);
+int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
+                            void* d_scratch, int32_t* d_oz_ptr, int32_t* d_out_nnz, int32_t* h_out_nnz,
+                            void* stream);
+
+/* Strided sparse conv, step 2: output depth indices, rules and neighbour tables.
+ * ref: getOzIndicesAndRulesKernel, src/sphconv/rules.cu:156-228,465-485.  Output rows are numbered in
+ * ascending (b,oX,oY,oZ) exactly as rules.cu:434-443 numbers them.
+ *   d_oz_idx  int32 [out_nnz]
+ *   d_nbr     int32 [KV, out_nnz]  input row per (offset, output row) or -1          (may be null)
+ *   d_nbr_t   int32 [KV, nnz]      output row per (offset, input row) or -1, for dgrad (may be null) */
+int sph_rules_strided_fill(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
+                           const void* d_scratch, const int32_t* d_oz_ptr, int64_t out_nnz,
+                           int32_t tile_n_max, int32_t* d_oz_idx, int32_t* d_rules, int32_t* d_rule_size,
+                           int32_t* d_nbr, int32_t* d_nbr_t, int fill_unused, int32_t* d_status, void* stream);
+
+/* Neighbour tables from a reference-format rules tensor (for rules that did not come from this library).
+ * ref: the consumer side of the format, include/sphconv/iterator.cu.h:147-181 (reads rules[t][k][0|1][v], v < ruleSize).
+ *   d_nbr   int32 [KV, out_rows] (may be null)   d_nbr_t int32 [KV, in_rows] (may be null) */
+int sph_rules_to_nbr(const int32_t* d_rules, const int32_t* d_rule_size, int32_t n_tile, int32_t kv,
+                     int32_t tile_n_max, int64_t in_rows, int64_t out_rows, int32_t* d_nbr, int32_t* d_nbr_t,
+                     int32_t* d_status, void* stream);
+
+/* ---- convolution ------------------------------------------------------------------------------ */
+
+/* Weight image for the tensor-core kernels.  d_weight is [KV, K, N] row-major in `dtype`
+ * (K = channels of the gathered rows, N = channels produced).  The packed image has
+ * sph_packed_weight_bytes() bytes. */
+int64_t sph_packed_weight_bytes(int dtype, int32_t kv, int32_t k_ch, int32_t n_ch);
+int sph_pack_weight(const void* d_weight, int dtype, int32_t kv, int32_t k_ch, int32_t n_ch, void* d_packed,
+                    void* stream);
+
+/* 1 when sph_conv_gather runs the tcgen05 kernel for this combination, 0 when it runs the CUDA-core kernel. */
+int sph_conv_uses_tensor_cores(int dtype, int32_t k_ch, int32_t n_ch);
+
+/* out[r,:] = epilogue( sum_k rows[ nbr[k][r], : ] @ weight[k] )   for r in [0, n_out)
+ * forward: ref rule_conv, src/sphconv/rule_conv.cu:286-336 (rows = feature, nbr = d_nbr, weight [KV,iC,oC]).
+ * dgrad:   ref rule_conv_d_feature, src/sphconv/rule_conv.cu:520-575 (rows = d_out, nbr = d_nbr_t,
+ *          weight = the [KV,oC,iC] transpose the reference's caller passes, sphconv/functional.py:70-74).
+ *   d_rows      [n_rows, k_ch] in `dtype`
+ *   d_weight    [KV, k_ch, n_ch] in `dtype` (CUDA-core kernel) ; d_packed: image from sph_pack_weight (tensor-core
+ *               kernel; may be null, then the CUDA-core kernel runs)
+ *   d_nbr       int32 [KV, n_out]
+ *   flip_k      != 0: offset k reads table row KV-1-k (dgrad of an odd-kernel submanifold layer reuses the
+ *               forward table this way)
+ *   d_scale/d_bias  float [n_ch] or null; relu != 0 applies max(0,.) ; epilogue = relu(acc*scale + bias)
+ *   out_dtype   dtype of d_out [n_out, n_ch]; F32/F16/BF16 accumulate in fp32, I8 accumulates in int32
+ *               and converts to float before the epilogue; I8 output rounds to nearest and saturates. */
+int sph_conv_gather(const void* d_rows, int dtype, int64_t n_rows, const void* d_weight, const void* d_packed,
+                    const int32_t* d_nbr, int64_t n_out, int32_t kv, int32_t k_ch, int32_t n_ch, int flip_k,
+                    const float* d_scale, const float* d_bias, int relu, void* d_out, int out_dtype,
+                    int32_t* d_status, void* stream);
+
+/* d_weight[k] (+)= rows[nbr[k][r], :]^T @ d_out[r, :] summed over r.
+ * ref: rule_conv_d_weight, src/sphconv/rule_conv.cu:469-518 (per-tile partials + torch::sum there; one fp32
+ * accumulation buffer here).
+ *   d_dweight   float [KV, k_ch, n_ch]; zeroed first when zero_init != 0, else accumulated into */
+int sph_conv_wgrad(const void* d_rows, const void* d_dout, int dtype, int64_t n_rows, const int32_t* d_nbr,
+                   int64_t n_out, int32_t kv, int32_t k_ch, int32_t n_ch, float* d_dweight, int zero_init,
+                   int32_t* d_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPHCONV_B200_H_ */

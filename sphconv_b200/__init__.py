@@ -1,0 +1,14 @@
+"""sphconv_b200: the sphconv rule-generation + rule-driven sparse convolution path for B200 (sm_100a).
+
+Same public names as the reference package (sphconv/__init__.py): import it as
+``import sphconv_b200 as sphconv``.  All compute runs in the CUDA library behind
+``include/sphconv_b200.h``; importing works without a GPU, calling an op without the built library raises.
+"""
+from .conv import Conv3d, SparseConv3d, SubMConv3d
+from .modules import Sequential, SparseSequential, SphModule
+from .tensor import SparseConvTensor
+from .sphconv_cuda import config
+from ._capi import check_status
+
+__all__ = ["Conv3d", "SparseConv3d", "SubMConv3d", "Sequential", "SparseSequential", "SphModule",
+           "SparseConvTensor", "config", "check_status"]

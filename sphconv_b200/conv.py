@@ -1,0 +1,160 @@
+"""Sparse convolution modules (ref: sphconv/conv.py)."""
+import math
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+
+from . import sphconv_cuda as ops
+from .functional import ConvFunction
+from .modules import SphModule
+from .tensor import SparseConvTensor
+from .utils import _calculate_fan_in_and_fan_out, _triple, kaiming_uniform_, out_spatial
+
+
+def divUp(x, y):
+    return (x + y - 1) // y
+
+
+def get_tile_grid_shape(out_spatial_shape_DWH: List[int], tile_size: List[int]) -> List[int]:
+    """ref: sphconv/conv.py:32-38"""
+    return [divUp(out_spatial_shape_DWH[0], tile_size[0]), divUp(out_spatial_shape_DWH[1], tile_size[1])]
+
+
+class Convolution(SphModule):
+    """Base class: owns weight [k0,k1,k2,iC,oC] and the optional bias (ref: sphconv/conv.py:40-96)."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: List[int], stride: List[int],
+                 padding: List[int], dilation: List[int], groups: int, tile_size: List[int], bias: bool, subm: bool,
+                 name: str, indice_key: Optional[str] = None, **kwargs):
+        super().__init__(**kwargs)
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.kernel_size = kernel_size
+        self.stride = stride
+        self.padding = padding
+        self.dilation = dilation
+        self.groups = groups
+        self.tile_size = tile_size
+        self.subm = subm
+        self.indice_key = indice_key
+        self.name = name
+        self.weight = nn.Parameter(torch.empty((*kernel_size, in_channels, out_channels)))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_channels))
+        else:
+            self.register_parameter('bias', None)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        kaiming_uniform_(self.weight, a=math.sqrt(5))
+        if self.bias is not None:
+            fan_in, _ = _calculate_fan_in_and_fan_out(self.weight)
+            bound = 1 / math.sqrt(fan_in)
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def extra_repr(self):
+        s = '{in_channels}, {out_channels}, kernel_size={kernel_size}, stride={stride}'
+        if self.padding != (0,) * len(self.padding):
+            s += ', padding={padding}'
+        if self.dilation != (1,) * len(self.dilation):
+            s += ', dilation={dilation}'
+        if self.groups != 1:
+            s += ', groups={groups}'
+        if self.bias is None:
+            s += ', bias=False'
+        if self.subm is True:
+            s += ', subm={subm}'
+        return s.format(**self.__dict__)
+
+
+class Conv3d(Convolution):
+    """3-D sparse convolution on range-voxel tensors (ref: sphconv/conv.py:99-193).
+
+    Reference behaviour is the default: the bias parameter exists but is not applied
+    (sphconv/conv.py:182-185).  Two opt-in extensions: `apply_bias=True` adds it and
+    `activation='relu'` applies ReLU; without grad both are fused into the kernel's epilogue."""
+
+    def __init__(self, in_channels, out_channels, kernel_size=3, stride=1, padding=0, dilation=1, groups=1,
+                 bias=False, subm=False, tile_size=[2, 2], indice_key=None, name=None, apply_bias=False,
+                 activation=None, **kwargs):
+        kernel_size = _triple(kernel_size)
+        stride = _triple(stride)
+        padding = _triple(padding)
+        dilation = _triple(dilation)
+        assert groups == 1, "groups not supported yet"
+        assert activation in (None, 'relu')
+        super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, groups, tile_size, bias,
+                         subm, name, indice_key=indice_key, **kwargs)
+        self.apply_bias = apply_bias
+        self.activation = activation
+
+    def _rules(self, input: SparseConvTensor, in_shape, out_shape):
+        fn = ops.get_rules_subm if self.subm else ops.get_rules
+        oz_idx, oz_ptr, rules, rule_size = fn(input.z_idx, input.z_ptr, input.B, in_shape, out_shape,
+                                              self.kernel_size, self.stride, self.padding, self.dilation,
+                                              self.tile_size)
+        return oz_idx, oz_ptr, rules, rule_size, get_tile_grid_shape(out_shape, self.tile_size)
+
+    def forward(self, input: SparseConvTensor):
+        batch_size, in_channels = input.B, input.C
+        out_channels = self.weight.shape[4]
+        assert self.in_channels == in_channels, \
+            "input channel does not match Expect: {}, got {}".format(self.in_channels, in_channels)
+        in_shape = [input.D, input.W, input.H]
+        out_shape = in_shape
+        if not self.subm:
+            out_shape = out_spatial(in_shape, self.kernel_size, self.stride, self.padding, self.dilation)
+
+        datas = input.find_rule(self.indice_key) if self.indice_key is not None else None
+        if datas is None:
+            datas = self._rules(input, in_shape, out_shape)
+            if self.indice_key is not None:
+                input.rule_cache[self.indice_key] = datas
+        oz_idx, oz_ptr, rules, rule_size, tile_grid_shape = datas
+        self.rule_size = rule_size
+
+        weight = self.weight.view((-1, in_channels, out_channels))
+        if weight.dtype != input.feature.dtype and input.feature.dtype != torch.int8:
+            weight = weight.to(input.feature.dtype)
+        bias = self.bias if (self.apply_bias and self.bias is not None) else None
+        needs_grad = torch.is_grad_enabled() and (input.feature.requires_grad or self.weight.requires_grad)
+        if needs_grad:
+            out_feature = ConvFunction.apply(input.feature, weight, rules, rule_size, tile_grid_shape,
+                                             oz_idx.shape[0])
+            if bias is not None:
+                out_feature = out_feature + bias.to(out_feature.dtype)
+            if self.activation == 'relu':
+                out_feature = torch.relu(out_feature)
+        else:
+            weight = self._cached_packed(weight)
+            out_feature = ops.rule_conv(input.feature, weight, rules, rule_size, oz_idx.shape[0],
+                                        bias=None if bias is None else bias.detach().float(),
+                                        relu=self.activation == 'relu')
+        out_tensor = SparseConvTensor(out_feature, out_shape, batch_size, z_ptr=oz_ptr, z_idx=oz_idx)
+        out_tensor.rule_cache = input.rule_cache
+        return out_tensor
+
+    def _cached_packed(self, weight):
+        """Inference: keep the tensor-core weight image across calls while the parameter is unchanged."""
+        key = (self.weight._version, self.weight.data_ptr(), weight.dtype)
+        cached = getattr(self, "_w_cache", None)
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        w = weight.detach().contiguous()
+        ops._packed_weight(w)
+        self._w_cache = (key, w)
+        return w
+
+
+SparseConv3d = Conv3d
+
+
+class SubMConv3d(Conv3d):
+    """Submanifold convolution: output sites = input sites, padding forced to k//2 (ref: sphconv/conv.py:200-210)."""
+
+    def __init__(self, in_channels, out_channels, kernel_size=3, stride=1, padding=0, dilation=1, groups=1,
+                 bias=False, subm=False, indice_key=None, **kwargs):
+        super().__init__(in_channels, out_channels, kernel_size, subm=True, stride=stride, padding=padding,
+                         dilation=dilation, groups=groups, bias=bias, indice_key=indice_key, **kwargs)
+        self.padding = tuple([k // 2 for k in self.kernel_size])

@@ -1,0 +1,91 @@
+// extern "C" entry points that are pure dispatch (declared in include/sphconv_b200.h).
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace sph {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+// conv_generic.cu
+int conv_gather_generic(const void* rows, int dtype, int64_t n_rows, const void* weight, const int* nbr,
+                        int64_t n_out, int kv, int K, int N, int flip_k, const float* scale, const float* bias,
+                        int relu, void* out, int out_dtype, int* status, cudaStream_t st);
+int conv_wgrad_generic(const void* rows, const void* dout, int dtype, int64_t n_rows, const int* nbr,
+                       int64_t n_out, int kv, int K, int N, float* dw, int* status, cudaStream_t st);
+// conv_tc.cu
+int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* packed, const int* nbr, int64_t n_out,
+                   int kv, int K, int N, int flip_k, const float* scale, const float* bias, int relu, void* out,
+                   int out_dtype, int* status, cudaStream_t st);
+bool conv_tc_supported(int dtype, int kv, int K, int N);
+int64_t packed_weight_bytes(int dtype, int kv, int K, int N);
+int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cudaStream_t st);
+
+}  // namespace sph
+
+using namespace sph;
+
+extern "C" const char* sph_last_error(void) { return g_err; }
+extern "C" int sph_version(void) { return 100; }
+
+extern "C" int64_t sph_packed_weight_bytes(int dtype, int32_t kv, int32_t k_ch, int32_t n_ch) {
+  if (!conv_tc_supported(dtype, kv, k_ch, n_ch)) return 0;
+  return packed_weight_bytes(dtype, kv, k_ch, n_ch);
+}
+
+extern "C" int sph_pack_weight(const void* d_weight, int dtype, int32_t kv, int32_t k_ch, int32_t n_ch,
+                               void* d_packed, void* stream) {
+  SPH_CHECK_ARG(d_weight && d_packed, "null pointer");
+  return pack_weight(d_weight, dtype, kv, k_ch, n_ch, d_packed, (cudaStream_t)stream);
+}
+
+extern "C" int sph_conv_uses_tensor_cores(int dtype, int32_t k_ch, int32_t n_ch) {
+  return conv_tc_supported(dtype, 27, k_ch, n_ch) ? 1 : 0;
+}
+
+static bool out_dtype_ok(int dtype, int out_dtype) {
+  if (out_dtype < SPH_F32 || out_dtype > SPH_I8) return false;
+  if (out_dtype == SPH_I8 && dtype != SPH_I8) return false;
+  return true;
+}
+
+extern "C" int sph_conv_gather(const void* d_rows, int dtype, int64_t n_rows, const void* d_weight,
+                               const void* d_packed, const int32_t* d_nbr, int64_t n_out, int32_t kv, int32_t k_ch,
+                               int32_t n_ch, int flip_k, const float* d_scale, const float* d_bias, int relu,
+                               void* d_out, int out_dtype, int32_t* d_status, void* stream) {
+  SPH_CHECK_ARG(n_rows >= 0 && n_out >= 0 && kv > 0 && k_ch > 0 && n_ch > 0, "bad sizes");
+  SPH_CHECK_ARG(dtype >= SPH_F32 && dtype <= SPH_I8, "unknown dtype");
+  SPH_CHECK_ARG(out_dtype_ok(dtype, out_dtype), "unsupported output dtype for this input dtype");
+  if (n_out == 0) return SPH_OK;
+  SPH_CHECK_ARG(d_nbr && d_out && (d_weight || d_packed), "null pointer");
+  SPH_CHECK_ARG(n_rows == 0 || d_rows, "null rows");
+  SPH_CHECK_ARG(n_rows < 0x7fffffffLL && n_out < 0x7fffffffLL, "row ids are 32-bit");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (d_packed && conv_tc_supported(dtype, kv, k_ch, n_ch)) {
+    return conv_gather_tc(d_rows, dtype, n_rows, d_packed, d_nbr, n_out, kv, k_ch, n_ch, flip_k, d_scale, d_bias,
+                          relu, d_out, out_dtype, d_status, st);
+  }
+  SPH_CHECK_ARG(d_weight, "the CUDA-core kernel needs the unpacked weight");
+  return conv_gather_generic(d_rows, dtype, n_rows, d_weight, d_nbr, n_out, kv, k_ch, n_ch, flip_k, d_scale, d_bias,
+                             relu, d_out, out_dtype, d_status, st);
+}
+
+extern "C" int sph_conv_wgrad(const void* d_rows, const void* d_dout, int dtype, int64_t n_rows,
+                              const int32_t* d_nbr, int64_t n_out, int32_t kv, int32_t k_ch, int32_t n_ch,
+                              float* d_dweight, int zero_init, int32_t* d_status, void* stream) {
+  SPH_CHECK_ARG(n_rows >= 0 && n_out >= 0 && kv > 0 && k_ch > 0 && n_ch > 0, "bad sizes");
+  SPH_CHECK_ARG(d_dweight, "null gradient buffer");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (zero_init) SPH_CUDA(cudaMemsetAsync(d_dweight, 0, (size_t)kv * k_ch * n_ch * sizeof(float), st));
+  if (n_out == 0 || n_rows == 0) return SPH_OK;
+  SPH_CHECK_ARG(d_rows && d_dout && d_nbr, "null pointer");
+  return conv_wgrad_generic(d_rows, d_dout, dtype, n_rows, d_nbr, n_out, kv, k_ch, n_ch, d_dweight, d_status, st);
+}

@@ -1,0 +1,492 @@
+// Rule generation over the range-voxel format without a dense voxel grid.
+//
+// What the reference does with a dense int32 grid [B,H,W,D] plus one global atomic per pair
+// (src/sphconv/rules.cu:55-82,98-150,156-228,234-311) is done here with per-column searches:
+// an output voxel o and kernel offset k name exactly one candidate input voxel i = o*s - pad + k,
+// and "is i active, and which row is it" is a scan of the (short) input column that holds it.
+//
+//  * one CTA per output tile, one warp per kernel offset (round-robin when KV > warps);
+//  * the CTA stages the tile's output voxels (row id + coordinates) in shared memory once;
+//  * each warp walks that list 32 voxels at a time for its offset, ballots the hits and writes the
+//    (in,out) pairs to consecutive slots of its own list, so list order is deterministic
+//    (ascending output row inside a batch, batches in order) and no global atomics are used;
+//  * the same pass fills the neighbour tables nbr[k][out] / nbr_t[k][in] the convolution kernels read.
+#include "common.cuh"
+
+namespace sph {
+
+namespace {
+
+constexpr int kEmitWarps = 9;
+constexpr int kEmitThreads = kEmitWarps * 32;
+constexpr int kEmitCap = 1024;      // output voxels staged per pass
+constexpr int kEmitMaxRanges = 128; // (batch, tile row) ranges handled per group
+constexpr int kMaxKV = 343;         // 7x7x7
+
+__device__ __forceinline__ int col_start(const int* __restrict__ zp, int64_t c) {
+  return c == 0 ? 0 : __ldg(zp + c - 1);
+}
+
+// Row id of input voxel (b,ix,iy,iz) or -1.  Columns hold a handful of entries, so a linear scan wins.
+__device__ __forceinline__ int find_row(const int* __restrict__ zi, const int* __restrict__ zp, const Geom& g,
+                                        int b, int ix, int iy, int iz) {
+  int64_t c = ((int64_t)b * g.H + ix) * g.W + iy;
+  int s = col_start(zp, c);
+  int e = __ldg(zp + c);
+  for (int r = s; r < e; ++r) {
+    if (__ldg(zi + r) == iz) return r;
+  }
+  return -1;
+}
+
+// One CTA per output tile.  in_* describe the input tensor, out_* the output tensor (the same
+// arrays for a submanifold layer).
+__global__ void __launch_bounds__(kEmitThreads)
+emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, const int* __restrict__ out_zi,
+                  const int* __restrict__ out_zp, Geom g, int64_t in_nnz, int64_t out_nnz, int tile_n_max,
+                  int* __restrict__ rules, int* __restrict__ rule_size, int* __restrict__ nbr,
+                  int* __restrict__ nbr_t, int* __restrict__ status) {
+  __shared__ int s_cnt[kMaxKV];
+  __shared__ int s_rstart[kEmitMaxRanges];
+  __shared__ int s_roff[kEmitMaxRanges + 1];
+  __shared__ int s_vrow[kEmitCap];
+  __shared__ int s_vb[kEmitCap];
+  __shared__ unsigned s_vxy[kEmitCap];
+  __shared__ int s_voz[kEmitCap];
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int t = blockIdx.x;
+  const int th = t / g.tgW, tw = t % g.tgW;
+  const int ox0 = th * g.tH, oy0 = tw * g.tW;
+  const int tHe = min(g.tH, g.oH - ox0);
+  const int tWe = min(g.tW, g.oW - oy0);
+  const int R = g.B * tHe;  // (batch, tile row) ranges; each is one contiguous run of output rows
+
+  for (int k = tid; k < g.KV; k += kEmitThreads) s_cnt[k] = 0;
+  __syncthreads();
+
+  for (int rg = 0; rg < R; rg += kEmitMaxRanges) {
+    const int nr = min(kEmitMaxRanges, R - rg);
+    if (tid < nr) {
+      int r = rg + tid;
+      int b = r / tHe, dx = r % tHe;
+      int64_t c0 = ((int64_t)b * g.oH + (ox0 + dx)) * g.oW + oy0;
+      int s = col_start(out_zp, c0);
+      int e = __ldg(out_zp + c0 + tWe - 1);
+      s_rstart[tid] = s;
+      s_roff[tid + 1] = e - s;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      s_roff[0] = 0;
+      for (int i = 0; i < nr; ++i) s_roff[i + 1] += s_roff[i];
+    }
+    __syncthreads();
+    const int T = s_roff[nr];
+
+    for (int p0 = 0; p0 < T; p0 += kEmitCap) {
+      const int np = min(kEmitCap, T - p0);
+      // ---- stage the output voxels [p0, p0+np) of this range group
+      for (int v = tid; v < np; v += kEmitThreads) {
+        int gv = p0 + v;
+        int lo = 0, hi = nr;  // largest j with s_roff[j] <= gv
+        while (hi - lo > 1) {
+          int mid = (lo + hi) >> 1;
+          if (s_roff[mid] <= gv) lo = mid; else hi = mid;
+        }
+        int row = s_rstart[lo] + (gv - s_roff[lo]);
+        int r = rg + lo;
+        int b = r / tHe, dx = r % tHe;
+        int64_t c0 = ((int64_t)b * g.oH + (ox0 + dx)) * g.oW + oy0;
+        int dy = 0;
+        while (dy < tWe - 1 && __ldg(out_zp + c0 + dy) <= row) ++dy;
+        s_vrow[v] = row;
+        s_vb[v] = b;
+        s_vxy[v] = ((unsigned)(ox0 + dx) << 16) | (unsigned)(oy0 + dy);
+        s_voz[v] = __ldg(out_zi + row);
+      }
+      __syncthreads();
+
+      // ---- one warp per kernel offset
+      for (int k = warp; k < g.KV; k += kEmitWarps) {
+        const int kh = k / (g.KW * g.KD), kw = (k / g.KD) % g.KW, kd = k % g.KD;
+        int base = s_cnt[k];
+        int* lst_in = rules ? rules + ((int64_t)t * g.KV + k) * 2 * tile_n_max : nullptr;
+        int* lst_out = rules ? lst_in + tile_n_max : nullptr;
+        for (int c = 0; c < np; c += 32) {
+          const int v = c + lane;
+          int in_row = -1, out_row = -1;
+          if (v < np) {
+            out_row = s_vrow[v];
+            int b = s_vb[v];
+            unsigned xy = s_vxy[v];
+            int ix = (int)(xy >> 16) * g.sH - g.pH + kh;
+            int iy = (int)(xy & 0xffffu) * g.sW - g.pW + kw;
+            int iz = s_voz[v] * g.sD - g.pD + kd;
+            if (ix >= 0 && ix < g.H && iy >= 0 && iy < g.W && iz >= 0 && iz < g.D)
+              in_row = find_row(in_zi, in_zp, g, b, ix, iy, iz);
+            if (nbr) nbr[(int64_t)k * out_nnz + out_row] = in_row;
+          }
+          unsigned m = __ballot_sync(0xffffffffu, in_row >= 0);
+          if (in_row >= 0) {
+            int slot = base + __popc(m & ((1u << lane) - 1u));
+            if (lst_in) {
+              if (slot < tile_n_max) {
+                lst_in[slot] = in_row;
+                lst_out[slot] = out_row;
+              } else if (status) {
+                atomicOr(status, SPH_STATUS_RULE_OVERFLOW);
+              }
+            }
+            if (nbr_t) nbr_t[(int64_t)k * in_nnz + in_row] = out_row;
+          }
+          base += __popc(m);
+        }
+        if (lane == 0) s_cnt[k] = base;
+      }
+      __syncthreads();
+    }
+  }
+  if (rule_size) {
+    for (int k = tid; k < g.KV; k += kEmitThreads) rule_size[(int64_t)t * g.KV + k] = s_cnt[k];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Strided conv: output sparsity pattern.
+// Per output column a depth bitmask (ceil(oD/32) words) = OR over the KH*KW input columns that reach it
+// of the shifted/strided depth bits; popcount = column count; a three-kernel scan gives oz_ptr.
+// ---------------------------------------------------------------------------------------------
+constexpr int kScanThreads = 256;
+
+__device__ __forceinline__ int block_inclusive_scan(int v, int* s_warp /*[8]*/, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += n;
+  }
+  if (lane == 31) s_warp[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < (kScanThreads / 32) ? s_warp[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += n;
+    }
+    if (lane < (kScanThreads / 32)) s_warp[lane] = w;
+  }
+  __syncthreads();
+  if (warp > 0) v += s_warp[warp - 1];
+  if (total) *total = s_warp[kScanThreads / 32 - 1];
+  __syncthreads();
+  return v;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+strided_mask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, Geom g, int words, int64_t ncols,
+                    uint32_t* __restrict__ mask, int* __restrict__ counts, int* __restrict__ blocksum) {
+  __shared__ int s_warp[kScanThreads / 32];
+  const int64_t c = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
+  int count = 0;
+  if (c < ncols) {
+    const int oy = (int)(c % g.oW);
+    const int ox = (int)((c / g.oW) % g.oH);
+    const int b = (int)(c / ((int64_t)g.oW * g.oH));
+    for (int w = 0; w < words; ++w) {
+      uint32_t m = 0;
+      for (int kh = 0; kh < g.KH; ++kh) {
+        int ix = ox * g.sH - g.pH + kh;
+        if (ix < 0 || ix >= g.H) continue;
+        for (int kw = 0; kw < g.KW; ++kw) {
+          int iy = oy * g.sW - g.pW + kw;
+          if (iy < 0 || iy >= g.W) continue;
+          int64_t ci = ((int64_t)b * g.H + ix) * g.W + iy;
+          int s = col_start(zp, ci), e = __ldg(zp + ci);
+          for (int r = s; r < e; ++r) {
+            int z = __ldg(zi + r);
+            for (int kd = 0; kd < g.KD; ++kd) {
+              int num = z + g.pD - kd;
+              if (num < 0) break;
+              if (num % g.sD) continue;
+              int oz = num / g.sD;
+              if (oz < g.oD && (oz >> 5) == w) m |= 1u << (oz & 31);
+            }
+          }
+        }
+      }
+      mask[c * words + w] = m;
+      count += __popc(m);
+    }
+    counts[c] = count;
+  }
+  int total;
+  block_inclusive_scan(count, s_warp, &total);
+  if (threadIdx.x == 0) blocksum[blockIdx.x] = total;
+}
+
+// Single CTA: exclusive scan of the block sums in place, grand total to *out_total.
+__global__ void __launch_bounds__(kScanThreads)
+scan_blocksums_kernel(int* __restrict__ blocksum, int n, int* __restrict__ out_total) {
+  __shared__ int s_warp[kScanThreads / 32];
+  int carry = 0;
+  for (int base = 0; base < n; base += kScanThreads) {
+    int i = base + threadIdx.x;
+    int v = i < n ? blocksum[i] : 0;
+    int total;
+    int inc = block_inclusive_scan(v, s_warp, &total);
+    if (i < n) blocksum[i] = carry + inc - v;
+    carry += total;
+  }
+  if (threadIdx.x == 0) *out_total = carry;
+}
+
+// counts -> inclusive prefix (in place) using the scanned block sums.
+__global__ void __launch_bounds__(kScanThreads)
+scan_columns_kernel(int* __restrict__ counts, int64_t ncols, const int* __restrict__ blocksum) {
+  __shared__ int s_warp[kScanThreads / 32];
+  const int64_t c = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
+  int v = c < ncols ? counts[c] : 0;
+  int inc = block_inclusive_scan(v, s_warp, nullptr);
+  if (c < ncols) counts[c] = inc + blocksum[blockIdx.x];
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+write_oz_idx_kernel(const uint32_t* __restrict__ mask, const int* __restrict__ oz_ptr, int words, int64_t ncols,
+                    int* __restrict__ oz_idx) {
+  const int64_t c = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
+  if (c >= ncols) return;
+  int pos = c == 0 ? 0 : oz_ptr[c - 1];
+  for (int w = 0; w < words; ++w) {
+    uint32_t m = mask[c * words + w];
+    while (m) {
+      int bit = __ffs(m) - 1;
+      oz_idx[pos++] = w * 32 + bit;
+      m &= m - 1;
+    }
+  }
+}
+
+// rules [NTile,KV,2,tnm] -> neighbour tables; one warp per (tile,k) list.
+__global__ void rules_to_nbr_kernel(const int* __restrict__ rules, const int* __restrict__ rule_size, int n_lists,
+                                    int kv, int tnm, int64_t in_rows, int64_t out_rows, int* __restrict__ nbr,
+                                    int* __restrict__ nbr_t, int* __restrict__ status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t lst = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (lst >= n_lists) return;
+  const int k = (int)(lst % kv);
+  int n = rule_size[lst];
+  if (n > tnm) {
+    n = tnm;
+    if (status && lane == 0) atomicOr(status, SPH_STATUS_RULE_OVERFLOW);
+  }
+  const int* in = rules + lst * 2 * tnm;
+  const int* out = in + tnm;
+  for (int v = lane; v < n; v += 32) {
+    int i = in[v], o = out[v];
+    if (i < 0 || i >= in_rows || o < 0 || o >= out_rows) {
+      if (status) atomicOr(status, SPH_STATUS_BAD_INDEX);
+      continue;
+    }
+    if (nbr) nbr[(int64_t)k * out_rows + o] = i;
+    if (nbr_t) nbr_t[(int64_t)k * in_rows + i] = o;
+  }
+}
+
+int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int* out_zp, const Geom& g,
+                int64_t in_nnz, int64_t out_nnz, int tnm, int* rules, int* rule_size, int* nbr, int* nbr_t,
+                int fill_unused, int* status, cudaStream_t st) {
+  if (rules && fill_unused) {
+    SPH_CUDA(cudaMemsetAsync(rules, 0xFF, (size_t)g.nTile * g.KV * 2 * (size_t)tnm * sizeof(int), st));
+  }
+  if (nbr_t && in_nnz > 0) {
+    SPH_CUDA(cudaMemsetAsync(nbr_t, 0xFF, (size_t)g.KV * (size_t)in_nnz * sizeof(int), st));
+  }
+  emit_rules_kernel<<<g.nTile, kEmitThreads, 0, st>>>(in_zi, in_zp, out_zi, out_zp, g, in_nnz, out_nnz, tnm, rules,
+                                                      rule_size, nbr, nbr_t, status);
+  SPH_LAUNCH_CHECK();
+  return SPH_OK;
+}
+
+}  // namespace
+
+int make_geom(const sph_geom* s, Geom* o) {
+  SPH_CHECK_ARG(s != nullptr, "geometry is null");
+  Geom g;
+  g.B = s->B;
+  g.H = s->in_shape[0]; g.W = s->in_shape[1]; g.D = s->in_shape[2];
+  g.oH = s->out_shape[0]; g.oW = s->out_shape[1]; g.oD = s->out_shape[2];
+  g.KH = s->ksize[0]; g.KW = s->ksize[1]; g.KD = s->ksize[2];
+  g.sH = s->stride[0]; g.sW = s->stride[1]; g.sD = s->stride[2];
+  g.pH = s->padding[0]; g.pW = s->padding[1]; g.pD = s->padding[2];
+  g.tH = s->tile[0]; g.tW = s->tile[1];
+  SPH_CHECK_ARG(g.B > 0 && g.H > 0 && g.W > 0 && g.D > 0, "batch and input shape must be positive");
+  SPH_CHECK_ARG(g.oH > 0 && g.oW > 0 && g.oD > 0, "output shape must be positive");
+  SPH_CHECK_ARG(g.KH > 0 && g.KW > 0 && g.KD > 0, "kernel size must be positive");
+  SPH_CHECK_ARG(g.sH > 0 && g.sW > 0 && g.sD > 0, "stride must be positive");
+  SPH_CHECK_ARG(g.pH >= 0 && g.pW >= 0 && g.pD >= 0, "padding must be non-negative");
+  SPH_CHECK_ARG(g.tH > 0 && g.tW > 0, "tile size must be positive");
+  g.KV = g.KH * g.KW * g.KD;
+  if (g.KV > kMaxKV) {
+    set_error("kernel volume %d exceeds the maximum %d", g.KV, kMaxKV);
+    return SPH_ERR_LIMIT;
+  }
+  if (g.oH > 65535 || g.oW > 65535) {
+    set_error("output H/W beyond 65535 are not supported");
+    return SPH_ERR_LIMIT;
+  }
+  if ((int64_t)g.B * g.H * g.W > 0x7fffffffLL || (int64_t)g.B * g.oH * g.oW > 0x7fffffffLL) {
+    set_error("more than 2^31 columns");
+    return SPH_ERR_LIMIT;
+  }
+  g.tgH = div_up(g.oH, g.tH);
+  g.tgW = div_up(g.oW, g.tW);
+  g.nTile = g.tgH * g.tgW;
+  *o = g;
+  return SPH_OK;
+}
+
+}  // namespace sph
+
+using namespace sph;
+
+extern "C" int sph_out_spatial(const int32_t in_shape[3], const int32_t ksize[3], const int32_t stride[3],
+                               const int32_t padding[3], int32_t out_shape[3]) {
+  SPH_CHECK_ARG(in_shape && ksize && stride && padding && out_shape, "null argument");
+  for (int d = 0; d < 3; ++d) {
+    SPH_CHECK_ARG(stride[d] > 0 && ksize[d] > 0, "stride and kernel size must be positive");
+    // floor((i + 2p - (k-1) - 1)/s + 1) as the reference computes it in floating point
+    int num = in_shape[d] + 2 * padding[d] - (ksize[d] - 1) - 1;
+    int q = num >= 0 ? num / stride[d] : -((-num + stride[d] - 1) / stride[d]);
+    out_shape[d] = q + 1;
+  }
+  return SPH_OK;
+}
+
+extern "C" int sph_num_tiles(const sph_geom* s) {
+  Geom g;
+  int rc = make_geom(s, &g);
+  return rc != SPH_OK ? rc : g.nTile;
+}
+
+extern "C" int sph_tile_n_max(const sph_geom* s, int64_t nnz) {
+  Geom g;
+  int rc = make_geom(s, &g);
+  if (rc != SPH_OK) return rc;
+  SPH_CHECK_ARG(g.sH <= g.KH && g.sW <= g.KW, "stride larger than the kernel");
+  int in_th = g.sH * (g.tH - 1) + g.KH;
+  int in_tw = g.sW * (g.tW - 1) + g.KW;
+  // same expression, evaluation order and types as the reference: the int product is formed first,
+  // then multiplied by the double sparsity, then by 2
+  double sparsity = (double)nnz / (double)((int64_t)g.B * g.H * g.W * g.D);
+  double size = g.B * in_th * in_tw * g.D * sparsity * 2;
+  return (int)(size + 64) & (-1 << 4);
+}
+
+extern "C" int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* s,
+                              int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int32_t* d_nbr,
+                              int fill_unused, int32_t* d_status, void* stream) {
+  Geom g;
+  int rc = make_geom(s, &g);
+  if (rc != SPH_OK) return rc;
+  SPH_CHECK_ARG(d_z_ptr != nullptr && nnz >= 0 && (nnz == 0 || d_z_idx != nullptr), "null input");
+  SPH_CHECK_ARG(g.H == g.oH && g.W == g.oW && g.D == g.oD, "submanifold rules need out_shape == in_shape");
+  SPH_CHECK_ARG((d_rules == nullptr) == (d_rule_size == nullptr), "rules and rule_size go together");
+  SPH_CHECK_ARG(d_rules == nullptr || tile_n_max > 0, "tile_n_max must be positive");
+  return launch_emit(d_z_idx, d_z_ptr, d_z_idx, d_z_ptr, g, nnz, nnz, tile_n_max, d_rules, d_rule_size, d_nbr,
+                     nullptr, fill_unused, d_status, (cudaStream_t)stream);
+}
+
+namespace {
+struct StridedScratch {
+  int words;
+  int64_t ncols;
+  int nblk;
+  size_t mask_bytes, blocksum_bytes;
+};
+StridedScratch strided_layout(const Geom& g) {
+  StridedScratch s;
+  s.words = div_up(g.oD, 32);
+  s.ncols = (int64_t)g.B * g.oH * g.oW;
+  s.nblk = (int)div_up64(s.ncols, kScanThreads);
+  s.mask_bytes = ((size_t)s.ncols * s.words * sizeof(uint32_t) + 255) & ~(size_t)255;
+  s.blocksum_bytes = ((size_t)s.nblk * sizeof(int) + 255) & ~(size_t)255;
+  return s;
+}
+}  // namespace
+
+extern "C" int64_t sph_rules_strided_scratch_bytes(const sph_geom* s) {
+  Geom g;
+  int rc = make_geom(s, &g);
+  if (rc != SPH_OK) return rc;
+  StridedScratch l = strided_layout(g);
+  return (int64_t)(l.mask_bytes + l.blocksum_bytes);
+}
+
+extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz,
+                                       const sph_geom* s, void* d_scratch, int32_t* d_oz_ptr, int32_t* d_out_nnz,
+                                       int32_t* h_out_nnz, void* stream) {
+  Geom g;
+  int rc = make_geom(s, &g);
+  if (rc != SPH_OK) return rc;
+  SPH_CHECK_ARG(d_z_ptr && d_scratch && d_oz_ptr && d_out_nnz && (nnz == 0 || d_z_idx), "null argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  StridedScratch l = strided_layout(g);
+  uint32_t* mask = (uint32_t*)d_scratch;
+  int* blocksum = (int*)((char*)d_scratch + l.mask_bytes);
+  strided_mask_kernel<<<l.nblk, kScanThreads, 0, st>>>(d_z_idx, d_z_ptr, g, l.words, l.ncols, mask, d_oz_ptr,
+                                                       blocksum);
+  SPH_LAUNCH_CHECK();
+  scan_blocksums_kernel<<<1, kScanThreads, 0, st>>>(blocksum, l.nblk, d_out_nnz);
+  SPH_LAUNCH_CHECK();
+  scan_columns_kernel<<<l.nblk, kScanThreads, 0, st>>>(d_oz_ptr, l.ncols, blocksum);
+  SPH_LAUNCH_CHECK();
+  if (h_out_nnz) {
+    SPH_CUDA(cudaMemcpyAsync(h_out_nnz, d_out_nnz, sizeof(int), cudaMemcpyDeviceToHost, st));
+    SPH_CUDA(cudaStreamSynchronize(st));
+  }
+  return SPH_OK;
+}
+
+extern "C" int sph_rules_strided_fill(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz,
+                                      const sph_geom* s, const void* d_scratch, const int32_t* d_oz_ptr,
+                                      int64_t out_nnz, int32_t tile_n_max, int32_t* d_oz_idx, int32_t* d_rules,
+                                      int32_t* d_rule_size, int32_t* d_nbr, int32_t* d_nbr_t, int fill_unused,
+                                      int32_t* d_status, void* stream) {
+  Geom g;
+  int rc = make_geom(s, &g);
+  if (rc != SPH_OK) return rc;
+  SPH_CHECK_ARG(d_z_ptr && d_scratch && d_oz_ptr && (nnz == 0 || d_z_idx), "null argument");
+  SPH_CHECK_ARG(out_nnz >= 0 && (out_nnz == 0 || d_oz_idx), "oz_idx is null");
+  SPH_CHECK_ARG((d_rules == nullptr) == (d_rule_size == nullptr), "rules and rule_size go together");
+  SPH_CHECK_ARG(d_rules == nullptr || tile_n_max > 0, "tile_n_max must be positive");
+  cudaStream_t st = (cudaStream_t)stream;
+  StridedScratch l = strided_layout(g);
+  const uint32_t* mask = (const uint32_t*)d_scratch;
+  if (out_nnz > 0) {
+    write_oz_idx_kernel<<<l.nblk, kScanThreads, 0, st>>>(mask, d_oz_ptr, l.words, l.ncols, d_oz_idx);
+    SPH_LAUNCH_CHECK();
+  }
+  return launch_emit(d_z_idx, d_z_ptr, d_oz_idx, d_oz_ptr, g, nnz, out_nnz, tile_n_max, d_rules, d_rule_size,
+                     d_nbr, d_nbr_t, fill_unused, d_status, st);
+}
+
+extern "C" int sph_rules_to_nbr(const int32_t* d_rules, const int32_t* d_rule_size, int32_t n_tile, int32_t kv,
+                                int32_t tile_n_max, int64_t in_rows, int64_t out_rows, int32_t* d_nbr,
+                                int32_t* d_nbr_t, int32_t* d_status, void* stream) {
+  SPH_CHECK_ARG(d_rules && d_rule_size, "null rules");
+  SPH_CHECK_ARG(n_tile > 0 && kv > 0 && tile_n_max > 0 && in_rows >= 0 && out_rows >= 0, "bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (d_nbr && out_rows > 0) SPH_CUDA(cudaMemsetAsync(d_nbr, 0xFF, (size_t)kv * out_rows * sizeof(int), st));
+  if (d_nbr_t && in_rows > 0) SPH_CUDA(cudaMemsetAsync(d_nbr_t, 0xFF, (size_t)kv * in_rows * sizeof(int), st));
+  int64_t n_lists = (int64_t)n_tile * kv;
+  int threads = 256;
+  int64_t blocks = div_up64(n_lists * 32, threads);
+  rules_to_nbr_kernel<<<(unsigned)blocks, threads, 0, st>>>(d_rules, d_rule_size, (int)n_lists, kv, tile_n_max,
+                                                            in_rows, out_rows, d_nbr, d_nbr_t, d_status);
+  SPH_LAUNCH_CHECK();
+  return SPH_OK;
+}

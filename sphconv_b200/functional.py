@@ -1,0 +1,74 @@
+"""Autograd glue, same classes and call signatures as the reference's sphconv/functional.py."""
+from typing import List
+
+import torch
+
+from .sphconv_cuda import (init_tensor, init_tensor_backward, rule_conv, rule_conv_backward, to_dense,
+                           to_dense_backward)
+
+
+class ConvFunction(torch.autograd.Function):
+    """Rule-driven sparse 3-D convolution (ref: sphconv/functional.py:12-78).
+
+    forward(feature [NNZ,iC], weight [KV,iC,oC], rules, rule_size, tile_grid_shape, outNNZ) -> [outNNZ,oC]
+    backward returns (d_feature, d_weight, None, None, None, None)."""
+
+    @staticmethod
+    def forward(ctx, feature: torch.Tensor, weight: torch.Tensor, rules, rule_size, tile_grid_shape: List[int],
+                outNNZ: int):
+        if isinstance(rules, torch.Tensor):
+            ctx.save_for_backward(feature, weight, rules, rule_size)
+            ctx.rule_obj = None
+        else:  # rule set generated without the padded tensor: keep the table object itself
+            ctx.save_for_backward(feature, weight)
+            ctx.rule_obj = rules
+        ctx.tile_grid_shape = tile_grid_shape
+        return rule_conv(feature, weight, rules, rule_size, outNNZ)
+
+    @staticmethod
+    def backward(ctx, d_featureOut: torch.Tensor):
+        if ctx.rule_obj is None:
+            feature, weight, rules, rule_size = ctx.saved_tensors
+        else:
+            feature, weight = ctx.saved_tensors
+            rules, rule_size = ctx.rule_obj, None
+        # the op takes the [KV,oC,iC] transpose, as in the reference (sphconv/functional.py:70-74)
+        d_feature, d_weight = rule_conv_backward(
+            d_featureOut.contiguous(), feature, weight.permute(0, 2, 1).contiguous(), rules, rule_size,
+            ctx.tile_grid_shape)
+        return d_feature, d_weight, None, None, None, None
+
+
+class ToDenseFunction(torch.autograd.Function):
+    """[NNZ,C] rows -> dense [B,C,s0,s1,s2] (ref: sphconv/functional.py:81-106)."""
+
+    @staticmethod
+    def forward(ctx, feature: torch.Tensor, z_idx: torch.Tensor, z_ptr: torch.Tensor, shape: List[int]):
+        ctx.save_for_backward(z_idx, z_ptr)
+        B, C, D, H, W = shape  # the reference's names; the dense layout is [B, s0, s1, s2, C]
+        res = torch.zeros((B, D, W, H, C), device=feature.device, dtype=feature.dtype)
+        to_dense(feature, z_idx, z_ptr, D, res)
+        return res.permute((0, 4, 1, 2, 3)).contiguous()
+
+    @staticmethod
+    def backward(ctx, d_featureOut):
+        z_idx, z_ptr = ctx.saved_tensors
+        d_feature = to_dense_backward(d_featureOut.permute((0, 2, 3, 4, 1)).contiguous(), z_idx, z_ptr)
+        return d_feature, None, None, None
+
+
+class InitTensorFunction(torch.autograd.Function):
+    """COO -> range-voxel (ref: sphconv/functional.py:109-131)."""
+
+    @staticmethod
+    def forward(ctx, raw_feature: torch.Tensor, indices_bzyx: torch.Tensor, batchsize: int,
+                spatial_shape_HWD: List[int]):
+        feature_out, zidx, zptr, permutation = init_tensor(raw_feature, indices_bzyx, batchsize, spatial_shape_HWD)
+        ctx.save_for_backward(permutation)
+        ctx.mark_non_differentiable(zidx, zptr)
+        return feature_out, zidx, zptr
+
+    @staticmethod
+    def backward(ctx, d_featureOut, d_zidx, d_zptr):
+        permutation, = ctx.saved_tensors
+        return init_tensor_backward(d_featureOut, permutation), None, None, None

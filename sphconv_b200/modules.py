@@ -1,0 +1,83 @@
+"""Module containers (ref: sphconv/modules.py)."""
+import sys
+from collections import OrderedDict
+
+import torch
+from torch import nn
+
+
+class SphModule(nn.Module):
+    """Marker base: subclasses receive a SparseConvTensor inside Sequential (ref: sphconv/modules.py:35-40)."""
+
+    def __init__(self, **kwargs):
+        super().__init__(**kwargs)
+
+
+def is_sph_module(module):
+    return isinstance(module, SphModule)
+
+
+def is_sparse_conv(module):
+    from .conv import Convolution
+    return isinstance(module, Convolution)
+
+
+class Sequential(SphModule):
+    """Sequential container that hands the sparse tensor to sparse modules and only `.feature` to dense
+    ones such as BatchNorm1d / ReLU (ref: sphconv/modules.py:43-128)."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__()
+        if len(args) == 1 and isinstance(args[0], OrderedDict):
+            for key, module in args[0].items():
+                self.add_module(key, module)
+        else:
+            for idx, module in enumerate(args):
+                self.add_module(str(idx), module)
+        for name, module in kwargs.items():
+            if sys.version_info < (3, 6):
+                raise ValueError("kwargs only supported in py36+")
+            if name in self._modules:
+                raise ValueError("name exists.")
+            self.add_module(name, module)
+        self._sparity_dict = {}
+
+    def __getitem__(self, idx):
+        if not (-len(self) <= idx < len(self)):
+            raise IndexError('index {} is out of range'.format(idx))
+        if idx < 0:
+            idx += len(self)
+        return list(self._modules.values())[idx]
+
+    def __len__(self):
+        return len(self._modules)
+
+    def add(self, module, name=None):
+        if name is None:
+            name = str(len(self._modules))
+            if name in self._modules:
+                raise KeyError("name exists")
+        self.add_module(name, module)
+
+    def forward(self, input):
+        from .conv import Conv3d, SubMConv3d
+        from .tensor import SparseConvTensor
+        nvtx = torch.cuda.nvtx if torch.cuda.is_available() else None
+        for k, module in self._modules.items():
+            if is_sph_module(module):
+                assert isinstance(input, SparseConvTensor)
+                if nvtx is not None:
+                    tag = "SubMConv3d" if isinstance(module, SubMConv3d) else \
+                        "Conv3d" if isinstance(module, Conv3d) else "layer"
+                    nvtx.range_push("{}:{}".format(tag, k))
+                input = module(input)
+                if nvtx is not None:
+                    nvtx.range_pop()
+            elif isinstance(input, SparseConvTensor):
+                input.feature = module(input.feature)
+            else:
+                input = module(input)
+        return input
+
+
+SparseSequential = Sequential

@@ -1,0 +1,292 @@
+"""The nine operators of the reference's ``sphconv.sphconv_cuda`` pybind module
+(``src/sphconv/all.cpp:14-38``), same names, argument order and return values, over the C ABI.
+
+Differences a caller can see, all documented:
+  * feature dtypes fp32, fp16, bf16 and int8 are accepted (the reference hard-codes float);
+  * pairs inside one (tile,k) list come in a deterministic order (the reference's is atomics order);
+  * entries of ``rules`` past ``rule_size`` are -1 only when ``config.fill_unused_rules`` is set
+    (no consumer reads them, ``include/sphconv/iterator.cu.h:173-177``);
+  * errors raise ``RuntimeError`` instead of ``printf``/``exit``.
+
+``get_rules*`` attach the neighbour tables the convolution kernels read to the returned ``rules``
+tensor (attribute ``_sph``).  Rules without it - cloned, loaded from disk, made elsewhere - are
+converted on first use and the result is cached on the tensor until it is modified in place.
+"""
+import ctypes
+from typing import List, Optional
+
+import torch
+
+from . import _capi as C
+
+
+class config:
+    """Process-wide switches."""
+    fill_unused_rules = True   # -1 padding of `rules` as the reference (rules.cu:364-366)
+    materialize_rules = True   # False: module path skips the padded `rules` tensor (rules/rule_size come back None)
+    transposed_table = None    # None: build the dgrad table when grad mode is on; True/False forces it
+
+
+class _Tables:
+    """Neighbour tables of one rule set.  nbr[k, o] = input row or -1; nbr_t[k, i] = output row or -1."""
+    __slots__ = ("nbr", "nbr_t", "n_in", "n_out", "version", "symmetric")
+
+    def __init__(self, nbr, nbr_t, n_in, n_out, version, symmetric):
+        self.nbr, self.nbr_t, self.n_in, self.n_out = nbr, nbr_t, n_in, n_out
+        self.version, self.symmetric = version, symmetric
+
+
+def _want_transposed():
+    if config.transposed_table is None:
+        return torch.is_grad_enabled()
+    return bool(config.transposed_table)
+
+
+def _check_common(zIndices, zPtr, dilation):
+    C.require_cuda(zIndices, zPtr)
+    if zIndices.dtype != torch.int32 or zPtr.dtype != torch.int32:
+        raise RuntimeError("z_idx and z_ptr must be int32")
+    if any(int(d) != 1 for d in dilation):
+        # the reference accepts the argument and ignores it (src/sphconv/rules.cu:40-41)
+        raise RuntimeError("dilation != 1 is not supported")
+
+
+def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
+                   outSpatialShape: List[int], kernelSize: List[int], stride: List[int], padding: List[int],
+                   dilation: List[int], tileSize: List[int]):
+    """ref: get_rules_subm, src/sphconv/rules.cu:326-390.  Returns [zIndices, zPtr, rules, ruleSize]
+    (the first two are the input objects, as in the reference)."""
+    _check_common(zIndices, zPtr, dilation)
+    lib = C.lib()
+    dev = zIndices.device
+    nnz = zIndices.shape[0]
+    g = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    kv = int(kernelSize[0]) * int(kernelSize[1]) * int(kernelSize[2])
+    n_tile = C.check(lib.sph_num_tiles(ctypes.byref(g)))
+    rules = rule_size = None
+    tnm = 0
+    if config.materialize_rules:
+        tnm = C.check(lib.sph_tile_n_max(ctypes.byref(g), nnz))
+        rules = torch.empty((n_tile, kv, 2, tnm), dtype=torch.int32, device=dev)
+        rule_size = torch.empty((n_tile, kv), dtype=torch.int32, device=dev)
+    nbr = torch.empty((kv, nnz), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        C.check(lib.sph_rules_subm(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), tnm, C.ptr(rules),
+                                   C.ptr(rule_size), C.ptr(nbr), int(config.fill_unused_rules),
+                                   C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+    symmetric = all(int(k) % 2 == 1 and int(p) == int(k) // 2 and int(s) == 1
+                    for k, p, s in zip(kernelSize, padding, stride))
+    tables = _Tables(nbr, None, nnz, nnz, rules._version if rules is not None else 0, symmetric)
+    if rules is not None:
+        rules._sph = tables
+        return [zIndices, zPtr, rules, rule_size]
+    return [zIndices, zPtr, tables, None]
+
+
+def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
+              outSpatialShape: List[int], kernelSize: List[int], stride: List[int], padding: List[int],
+              dilation: List[int], tileSize: List[int]):
+    """ref: get_rules, src/sphconv/rules.cu:405-486.  Returns [ozIndices, ozPtr, rules, ruleSize]."""
+    _check_common(zIndices, zPtr, dilation)
+    lib = C.lib()
+    dev = zIndices.device
+    nnz = zIndices.shape[0]
+    g = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    kv = int(kernelSize[0]) * int(kernelSize[1]) * int(kernelSize[2])
+    n_tile = C.check(lib.sph_num_tiles(ctypes.byref(g)))
+    scratch_bytes = C.check(lib.sph_rules_strided_scratch_bytes(ctypes.byref(g)))
+    scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=dev)
+    oz_ptr = torch.empty((batchSize, int(outSpatialShape[0]), int(outSpatialShape[1])), dtype=torch.int32, device=dev)
+    d_count = torch.empty((1,), dtype=torch.int32, device=dev)
+    h_count = ctypes.c_int32(0)
+    status = C.status_tensor(dev)
+    with torch.cuda.device(dev):
+        st = C.stream_ptr(dev)
+        C.check(lib.sph_rules_strided_count(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), C.ptr(scratch),
+                                            C.ptr(oz_ptr), C.ptr(d_count), ctypes.byref(h_count), st))
+        out_nnz = int(h_count.value)
+        oz_idx = torch.empty((out_nnz,), dtype=torch.int32, device=dev)
+        rules = rule_size = None
+        tnm = 0
+        if config.materialize_rules:
+            tnm = C.check(lib.sph_tile_n_max(ctypes.byref(g), nnz))
+            rules = torch.empty((n_tile, kv, 2, tnm), dtype=torch.int32, device=dev)
+            rule_size = torch.empty((n_tile, kv), dtype=torch.int32, device=dev)
+        nbr = torch.empty((kv, out_nnz), dtype=torch.int32, device=dev)
+        nbr_t = torch.empty((kv, nnz), dtype=torch.int32, device=dev) if _want_transposed() else None
+        C.check(lib.sph_rules_strided_fill(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), C.ptr(scratch),
+                                           C.ptr(oz_ptr), out_nnz, tnm, C.ptr(oz_idx), C.ptr(rules), C.ptr(rule_size),
+                                           C.ptr(nbr), C.ptr(nbr_t), int(config.fill_unused_rules), C.ptr(status), st))
+    tables = _Tables(nbr, nbr_t, nnz, out_nnz, rules._version if rules is not None else 0, False)
+    if rules is not None:
+        rules._sph = tables
+        return [oz_idx, oz_ptr, rules, rule_size]
+    return [oz_idx, oz_ptr, tables, None]
+
+
+def _tables_for(rules, rule_size, n_in: int, n_out: int, need_t: bool) -> _Tables:
+    """Neighbour tables of a rule set: the ones attached by get_rules*, or a conversion of the
+    reference-format tensors (cached on `rules`)."""
+    if isinstance(rules, _Tables):
+        tb = rules
+    else:
+        tb = getattr(rules, "_sph", None)
+        if tb is not None and (tb.version != rules._version or tb.n_in != n_in or tb.n_out != n_out):
+            tb = None
+    if tb is not None and (not need_t or tb.nbr_t is not None or tb.symmetric):
+        return tb
+    if isinstance(rules, _Tables):
+        raise RuntimeError("this rule set was generated without the transposed table; enable grad mode (or "
+                           "config.transposed_table) before generating rules that backward will use")
+    C.require_cuda(rules, rule_size)
+    lib = C.lib()
+    dev = rules.device
+    n_tile, kv, _, tnm = rules.shape
+    nbr = tb.nbr if tb is not None else torch.empty((kv, n_out), dtype=torch.int32, device=dev)
+    nbr_t = torch.empty((kv, n_in), dtype=torch.int32, device=dev) if need_t else None
+    with torch.cuda.device(dev):
+        C.check(lib.sph_rules_to_nbr(C.ptr(rules), C.ptr(rule_size), n_tile, kv, tnm, n_in, n_out,
+                                     None if tb is not None else C.ptr(nbr), C.ptr(nbr_t),
+                                     C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+    new = _Tables(nbr, nbr_t, n_in, n_out, rules._version, tb.symmetric if tb is not None else False)
+    rules._sph = new
+    return new
+
+
+def _packed_weight(weight: torch.Tensor):
+    """UMMA image of a [KV, K, N] weight, or None when the CUDA-core kernel will run.  Cached on the tensor."""
+    code = C.DTYPE_CODE[weight.dtype]
+    kv, k_ch, n_ch = weight.shape
+    lib = C.lib()
+    nbytes = lib.sph_packed_weight_bytes(code, kv, k_ch, n_ch)
+    if nbytes <= 0:
+        return None
+    cached = getattr(weight, "_sph_packed", None)
+    if cached is not None and cached[0] == weight._version:
+        return cached[1]
+    packed = torch.empty((nbytes,), dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        C.check(lib.sph_pack_weight(C.ptr(weight), code, kv, k_ch, n_ch, C.ptr(packed), C.stream_ptr(weight.device)))
+    weight._sph_packed = (weight._version, packed)
+    return packed
+
+
+def _gather(rows, weight, nbr, n_out, flip_k, scale, bias, relu, out_dtype):
+    C.require_cuda(rows, weight, nbr, scale, bias)
+    if rows.dtype not in C.DTYPE_CODE:
+        raise RuntimeError("unsupported feature dtype %s" % rows.dtype)
+    if weight.dtype != rows.dtype:
+        raise RuntimeError("feature (%s) and weight (%s) dtypes differ" % (rows.dtype, weight.dtype))
+    kv, k_ch, n_ch = weight.shape
+    if rows.dim() != 2 or rows.shape[1] != k_ch:
+        raise RuntimeError("feature has %d channels, weight expects %d" % (rows.shape[-1], k_ch))
+    if out_dtype is None:
+        out_dtype = torch.float32 if rows.dtype == torch.int8 else rows.dtype
+    dev = rows.device
+    out = torch.empty((n_out, n_ch), dtype=out_dtype, device=dev)
+    if n_out == 0:
+        return out
+    packed = _packed_weight(weight)
+    for v in (scale, bias):
+        if v is not None and (v.dtype != torch.float32 or v.numel() != n_ch):
+            raise RuntimeError("scale / bias must be float32 [out_channels]")
+    with torch.cuda.device(dev):
+        C.check(C.lib().sph_conv_gather(C.ptr(rows), C.DTYPE_CODE[rows.dtype], rows.shape[0], C.ptr(weight),
+                                        C.ptr(packed), C.ptr(nbr), n_out, kv, k_ch, n_ch, int(bool(flip_k)),
+                                        C.ptr(scale), C.ptr(bias), int(bool(relu)), C.ptr(out),
+                                        C.DTYPE_CODE[out_dtype], C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+    return out
+
+
+def rule_conv(feature: torch.Tensor, weight: torch.Tensor, rules, ruleSize, outNNZ: int, *,
+              scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, relu: bool = False,
+              out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """ref: rule_conv, src/sphconv/rule_conv.cu:286-336.  feature [NNZ,iC], weight [KV,iC,oC] ->
+    [outNNZ,oC].  Keyword arguments are extensions (fused epilogue relu(acc*scale + bias), output dtype)."""
+    tb = _tables_for(rules, ruleSize, feature.shape[0], int(outNNZ), need_t=False)
+    return _gather(feature, weight, tb.nbr, int(outNNZ), False, scale, bias, relu, out_dtype)
+
+
+def rule_conv_d_feature(feature: torch.Tensor, weight: torch.Tensor, rules, ruleSize,
+                        tile_grid_shape: List[int], outNNZ: int) -> torch.Tensor:
+    """ref: rule_conv_d_feature, src/sphconv/rule_conv.cu:520-575.  `feature` is the upstream gradient
+    [outNNZ_fwd, oC], `weight` the [KV,oC,iC] transpose, `outNNZ` the number of input rows; returns [outNNZ, iC].
+    tile_grid_shape is accepted for signature compatibility (the reference needs it for its 9-colour launches)."""
+    n_in = int(outNNZ)
+    tb = _tables_for(rules, ruleSize, n_in, feature.shape[0], need_t=True)
+    if tb.nbr_t is not None:
+        return _gather(feature, weight, tb.nbr_t, n_in, False, None, None, False, None)
+    # odd-kernel submanifold layer: (i,o) at k  <=>  (o,i) at KV-1-k, so the forward table serves
+    return _gather(feature, weight, tb.nbr, n_in, True, None, None, False, None)
+
+
+def rule_conv_d_weight(feature: torch.Tensor, d_featureOut: torch.Tensor, rules, ruleSize) -> torch.Tensor:
+    """ref: rule_conv_d_weight, src/sphconv/rule_conv.cu:469-518.  Returns float32 [KV,iC,oC]."""
+    C.require_cuda(feature, d_featureOut)
+    if feature.dtype != d_featureOut.dtype:
+        raise RuntimeError("feature and gradient dtypes differ")
+    tb = _tables_for(rules, ruleSize, feature.shape[0], d_featureOut.shape[0], need_t=False)
+    kv = tb.nbr.shape[0]
+    k_ch, n_ch = feature.shape[1], d_featureOut.shape[1]
+    dev = feature.device
+    dw = torch.empty((kv, k_ch, n_ch), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        C.check(C.lib().sph_conv_wgrad(C.ptr(feature), C.ptr(d_featureOut), C.DTYPE_CODE[feature.dtype],
+                                       feature.shape[0], C.ptr(tb.nbr), d_featureOut.shape[0], kv, k_ch, n_ch,
+                                       C.ptr(dw), 1, C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+    return dw
+
+
+def rule_conv_backward(d_featureOut: torch.Tensor, feature: torch.Tensor, weight: torch.Tensor, rules, ruleSize,
+                       tile_grid_shape: List[int]):
+    """ref: rule_conv_backward, src/sphconv/rule_conv.cu:577-597.  `weight` is [KV,oC,iC].
+    Returns [d_feature [NNZ,iC], d_weight [KV,iC,oC]] in the dtype of `feature`."""
+    d_featureOut = d_featureOut.contiguous()
+    d_feature = rule_conv_d_feature(d_featureOut, weight, rules, ruleSize, tile_grid_shape, feature.shape[0])
+    d_weight = rule_conv_d_weight(feature, d_featureOut, rules, ruleSize).to(feature.dtype)
+    return [d_feature, d_weight]
+
+
+# ---- adjacent tensor ops (not on the accelerated path: COO <-> range-voxel, densify) -----------------
+
+def _row_columns(zPtr: torch.Tensor):
+    zp = zPtr.reshape(-1).to(torch.int64)
+    counts = torch.diff(zp, prepend=zp.new_zeros(1))
+    return torch.repeat_interleave(torch.arange(zp.shape[0], device=zp.device), counts)
+
+
+def init_tensor(feature: torch.Tensor, indicesBZYX: torch.Tensor, batchSize: int, spatialShape: List[int]):
+    """ref: init_tensor, src/sphconv/tensor.cu:78-127.  COO (b, s0, s1, s2) -> range-voxel.
+    Returns [feature', zIndices, zPtr, permutation] with permutation[n] = new row of input row n.
+    Rows inside a column are ordered by depth (the reference's order is atomics arrival order)."""
+    C.require_cuda(feature, indicesBZYX)
+    H, W, D = [int(s) for s in spatialShape]
+    idx = indicesBZYX.to(torch.int64)
+    col = (idx[:, 0] * H + idx[:, 1]) * W + idx[:, 2]
+    order = torch.argsort(col * D + idx[:, 3], stable=True)
+    permutation = torch.empty_like(order)
+    permutation[order] = torch.arange(order.shape[0], device=order.device)
+    z_idx = idx[order, 3].to(torch.int32)
+    counts = torch.bincount(col, minlength=batchSize * H * W)
+    z_ptr = torch.cumsum(counts, 0).to(torch.int32).reshape(batchSize, H, W)
+    return [feature[order].contiguous(), z_idx, z_ptr, permutation.to(torch.int32)]
+
+
+def init_tensor_backward(d_featureOut: torch.Tensor, permutation: torch.Tensor) -> torch.Tensor:
+    """ref: init_tensor_backward, src/sphconv/tensor.cu:147-162: d_feature[n] = d_featureOut[permutation[n]]."""
+    return d_featureOut[permutation.to(torch.int64)].contiguous()
+
+
+def to_dense(feature: torch.Tensor, zIndices: torch.Tensor, zPtr: torch.Tensor, D: int, out: torch.Tensor):
+    """ref: to_dense, src/sphconv/tensor.cu:222-264.  Fills out [B,H,W,D,C] in place and returns it.
+    The integer argument is unused, as in the reference kernel, which takes every size from `out`."""
+    col = _row_columns(zPtr)
+    out.view(-1, out.shape[3], out.shape[4])[col, zIndices.to(torch.int64)] = feature
+    return out
+
+
+def to_dense_backward(d_featureOut: torch.Tensor, zIndices: torch.Tensor, zPtr: torch.Tensor) -> torch.Tensor:
+    """ref: to_dense_backward, src/sphconv/tensor.cu:266-309.  d_featureOut [B,H,W,D,C] -> [NNZ,C]."""
+    col = _row_columns(zPtr)
+    D, Cc = d_featureOut.shape[3], d_featureOut.shape[4]
+    return d_featureOut.reshape(-1, D, Cc)[col, zIndices.to(torch.int64)].contiguous()

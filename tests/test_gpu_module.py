@@ -1,0 +1,120 @@
+"""Module-level API (SparseConvTensor, SubMConv3d, Conv3d, Sequential, autograd) against dense torch conv3d,
+the ground truth of the reference's test/test_module.py, test/test_grad.py and test/test_util.py."""
+import numpy as np
+import pytest
+import torch
+
+import sphconv_b200 as sphconv
+from oracle import dense_ref
+from sphconv_b200 import synthetic
+
+from gpu_util import DEV
+
+pytestmark = pytest.mark.gpu
+
+
+def _coo(rng, B, shape, dens):
+    occ = rng.random((B, *shape)) < dens
+    idx = np.stack(np.nonzero(occ), axis=1).astype(np.int32)
+    rng.shuffle(idx)                       # COO rows in arbitrary order
+    return idx
+
+
+def test_init_tensor_and_dense_roundtrip():
+    rng = np.random.default_rng(0)
+    B, shape, C = 3, [6, 7, 9], 5
+    idx = _coo(rng, B, shape, 0.3)
+    feat = rng.standard_normal((idx.shape[0], C)).astype(np.float32)
+    t = sphconv.SparseConvTensor(torch.as_tensor(feat, device=DEV), shape, B, indices=torch.as_tensor(idx, device=DEV))
+    assert t.shape == [B, C, *shape]
+    dense = t.dense().cpu()
+    want = torch.zeros((B, C, *shape))
+    want[idx[:, 0], :, idx[:, 1], idx[:, 2], idx[:, 3]] = torch.as_tensor(feat)
+    assert torch.equal(dense, want)
+    zp = t.z_ptr.cpu().numpy().reshape(-1)
+    assert zp[-1] == idx.shape[0] and (np.diff(zp) >= 0).all()
+    # gradient flows through dense() and the COO reorder back to the raw rows
+    raw = torch.as_tensor(feat, device=DEV).requires_grad_(True)
+    t2 = sphconv.SparseConvTensor(raw, shape, B, indices=torch.as_tensor(idx, device=DEV))
+    g = torch.as_tensor(rng.standard_normal((B, C, *shape)).astype(np.float32), device=DEV)
+    (t2.dense() * g).sum().backward()
+    want_g = g.cpu()[idx[:, 0], :, idx[:, 1], idx[:, 2], idx[:, 3]]
+    assert torch.allclose(raw.grad.cpu(), want_g)
+
+
+@pytest.mark.parametrize("subm", [True, False])
+@pytest.mark.parametrize("iC,oC", [(4, 16), (16, 16), (32, 64)])
+def test_module_forward_backward_vs_dense(subm, iC, oC):
+    rng = np.random.default_rng(1)
+    B, shape = 2, [8, 10, 12]
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.3)
+    feat = rng.standard_normal((z_idx.shape[0], iC)).astype(np.float32)
+    if subm:
+        layer = sphconv.SubMConv3d(iC, oC, 3, bias=False).to(DEV)
+        st, pd = [1, 1, 1], [1, 1, 1]
+    else:
+        layer = sphconv.Conv3d(iC, oC, 3, stride=2, padding=1, bias=False).to(DEV)
+        st, pd = [2, 2, 2], [1, 1, 1]
+    f = torch.as_tensor(feat, device=DEV).requires_grad_(True)
+    x = sphconv.SparseConvTensor(f, shape, B, z_idx=torch.as_tensor(z_idx, device=DEV), z_ptr=torch.as_tensor(z_ptr, device=DEV))
+    y = layer(x)
+    yd = y.dense()
+    w5 = layer.weight.detach().cpu().numpy()
+    up = rng.standard_normal(tuple(yd.shape)).astype(np.float32)
+    if subm:   # gradient only at active sites
+        mask = (dense_ref.densify(np.ones((z_idx.shape[0], 1), np.float32), z_idx, z_ptr, B, shape) != 0).numpy()
+        up = up * mask
+    (yd * torch.as_tensor(up, device=DEV)).sum().backward()
+    ref_y, ref_dx, ref_dw = dense_ref.dense_conv_grads(feat, w5, lambda t: torch.as_tensor(up).double(), z_idx, z_ptr,
+                                                       B, shape, st, pd)
+    if subm:
+        ref_y = ref_y * torch.as_tensor(mask)
+    assert torch.allclose(yd.cpu().double(), ref_y, atol=1e-4)
+    assert torch.allclose(f.grad.cpu().double(), ref_dx, atol=1e-4)
+    assert torch.allclose(layer.weight.grad.cpu().double(), ref_dw, atol=1e-3)
+
+
+def test_sequential_rule_cache_and_dense_modules():
+    rng = np.random.default_rng(2)
+    B, shape = 2, [8, 10, 12]
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.3)
+    feat = torch.as_tensor(rng.standard_normal((z_idx.shape[0], 4)).astype(np.float32), device=DEV)
+    net = sphconv.Sequential(
+        sphconv.SubMConv3d(4, 16, 3, indice_key="subm0"), torch.nn.ReLU(),
+        sphconv.SubMConv3d(16, 16, 3, indice_key="subm0"), torch.nn.ReLU(),
+        sphconv.SparseConv3d(16, 32, 3, stride=2, padding=1),
+    ).to(DEV)
+    x = sphconv.SparseConvTensor(feat, shape, B, z_idx=torch.as_tensor(z_idx, device=DEV), z_ptr=torch.as_tensor(z_ptr, device=DEV))
+    with torch.no_grad():
+        y = net(x)
+    assert "subm0" in y.rule_cache and len(y.rule_cache) == 1
+    assert y.feature.shape[1] == 32 and y.shape[2:] == [4, 5, 6]
+    # dense reference of the same stack
+    d = dense_ref.densify(feat.cpu().numpy(), z_idx, z_ptr, B, shape)
+    mask = dense_ref.densify(np.ones((z_idx.shape[0], 1), np.float32), z_idx, z_ptr, B, shape) != 0
+    convs = [m for m in net._modules.values() if isinstance(m, sphconv.Conv3d)]
+    for i, m in enumerate(convs):
+        w = m.weight.detach().cpu().permute(4, 3, 0, 1, 2).contiguous()
+        if m.subm:
+            d = torch.relu(torch.nn.functional.conv3d(d, w, None, 1, 1)) * mask
+        else:
+            d = torch.nn.functional.conv3d(d, w, None, 2, 1)
+    assert torch.allclose(y.dense().cpu(), d, atol=1e-4)
+
+
+def test_fused_bias_relu_extension_matches_unfused():
+    rng = np.random.default_rng(3)
+    B, shape = 1, [8, 10, 12]
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.3)
+    feat = torch.as_tensor(rng.standard_normal((z_idx.shape[0], 16)).astype(np.float32), device=DEV).half()
+    layer = sphconv.SubMConv3d(16, 32, 3, bias=True, apply_bias=True, activation='relu').to(DEV).half()
+    plain = sphconv.SubMConv3d(16, 32, 3, bias=True).to(DEV).half()
+    plain.load_state_dict(layer.state_dict())
+    mk = lambda: sphconv.SparseConvTensor(feat, shape, B, z_idx=torch.as_tensor(z_idx, device=DEV), z_ptr=torch.as_tensor(z_ptr, device=DEV))
+    with torch.no_grad():
+        fused = layer(mk()).feature
+        ref = torch.relu(plain(mk()).feature.float() + plain.bias.float())
+    assert torch.allclose(fused.float(), ref, atol=2e-2, rtol=1e-2)
+    # the reference applies no bias by default (sphconv/conv.py:182-185)
+    with torch.no_grad():
+        assert not torch.allclose(plain(mk()).feature.float(), ref)
