@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Benchmark of the sphconv hot path on B200: rule generation + rule-driven sparse convolution of the
+SECOND-style 8-layer encoder over synthetic range-voxel scans.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg5|cfg4] [--impl reference]
+
+One step = one pass of the whole path over one batch of scans: five rule sets (the SubM pairs share
+theirs) and eight convolutions.  Rank r of N processes its own scans (no data-path collective).
+Prints ONE JSON line on rank 0.  `value` is scans/s with inputs resident in HBM; `e2e` is the same
+through the module API with pinned HOST buffers (H2D of z_ptr/z_idx/features and D2H of the output
+features and their oz_ptr/oz_idx inside the timed region).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from sphconv_b200 import synthetic  # noqa: E402
+
+DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p["bf16_tflops"], tflops_sustained=p.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.rows = []
+        self.proc = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", uuid, "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return None
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.05 and len(r) >= 7] or \
+               [r for t, r in self.rows if len(r) >= 7]
+        if not rows:
+            return None
+        sm = sorted(float(r[0]) for r in rows)
+        reasons = set()
+        for r in rows:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][1]), "samples": len(rows),
+                "reasons": sorted(reasons)}
+
+
+def workload(name, world, rank, batch_override):
+    cfg = dict(synthetic.CONFIGS[name])
+    if name == "cfg5":          # 64 scans sharded over the ranks (fixed total work)
+        B = batch_override or max(1, 64 // world)
+        scaling = "strong"
+    else:                       # every rank runs the configuration's batch (fixed per-GPU work)
+        B = batch_override or cfg["B"]
+        scaling = "weak"
+    return cfg, B, scaling, rank * B
+
+
+def cpu_dense_scan(cfg, scan_id, threads, w_div=1):
+    """The reference's CPU check for this path - dense fp32 conv3d over the densified grid
+    (test/test_rules.py:14-60, test/test_grad.py:7-36) - for ONE scan of the workload, or for a strip of
+    1/w_div of its azimuth columns (dense work is proportional to the grid, whatever the sparsity).
+    Returns (seconds, checksum)."""
+    from oracle import dense_ref
+    from sphconv_b200.encoder import encoder8_parameters
+    cfg = dict(cfg)
+    cfg["shape"] = [cfg["shape"][0], cfg["shape"][1] // w_div, cfg["shape"][2]]
+    b = synthetic.make_batch(cfg, batch=1, first_scan=scan_id)
+    params = encoder8_parameters()
+    torch.set_num_threads(threads)
+    with torch.no_grad():
+        t0 = time.perf_counter()
+        y, _ = dense_ref.encoder_dense_forward(b["feature"], b["z_idx"], b["z_ptr"], 1, cfg["shape"],
+                                               synthetic.ENCODER8, params)
+        dt = time.perf_counter() - t0
+    return dt, float(y.abs().sum())
+
+
+def run_reference(args):
+    """Reference arm: the path's CPU form on the host cores (the reference has no CPU implementation of its
+    CUDA kernels; its tests check them against dense torch conv3d, which is what is timed here)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = dict(synthetic.CONFIGS[args.workload])
+    threads = os.cpu_count() or 1
+    w_div = 8                   # one step = a 1/8-azimuth strip of one scan: about a second of host work
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, _ = cpu_dense_scan(cfg, i, threads, w_div)
+        if i >= args.warmup:
+            times.append(dt)
+    total = sum(times)
+    value = len(times) / w_div / total
+    sample = ("each step = a 1/%d azimuth strip (%dx%dx%d) of one %s scan through all 8 layers as dense fp32 conv3d "
+              "on the densified grid" % (w_div, cfg["shape"][0], cfg["shape"][1] // w_div, cfg["shape"][2], args.workload))
+    line = {
+        "impl": "reference", "metric": "backbone scans/sec", "value": value, "unit": "scans/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "%s: SECOND-style 8-layer encoder, dense fp32 on host cores" % args.workload,
+                   "shape": cfg["shape"], "scans_per_step": 1.0 / w_div},
+        "cpu_baseline": {"value": value, "unit": "scans/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "scans/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg3", choices=["cfg3"])
+    ap.add_argument("--batch", type=int, default=0, help="scans per rank per step (default: the configuration's)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    import sphconv_b200 as sphconv
+    from sphconv_b200 import _capi, profiling
+    from sphconv_b200.encoder import build_encoder8
+
+    cfg, B, scaling, first_scan = workload(args.workload, world, rank, args.batch)
+    dtype_name = {"cfg3": "fp16", "cfg4": "bf16", "cfg5": "fp16"}[args.workload]
+    dtype = DTYPES[dtype_name]
+    shape = cfg["shape"]
+    batch = synthetic.make_batch(cfg, batch=B, first_scan=first_scan)
+    h_feat = torch.as_tensor(batch["feature"]).to(dtype).pin_memory()
+    h_zidx = torch.as_tensor(batch["z_idx"]).pin_memory()
+    h_zptr = torch.as_tensor(batch["z_ptr"]).pin_memory()
+    d_feat, d_zidx, d_zptr = h_feat.to(dev), h_zidx.to(dev), h_zptr.to(dev)
+    net = build_encoder8(dtype=dtype, device=dev, fused=True).eval()
+    sphconv.config.fill_unused_rules = False   # entries of `rules` past rule_size are never read by the path
+    lib = _capi.lib()
+
+    def step_resident():
+        x = sphconv.SparseConvTensor(d_feat, shape, B, z_idx=d_zidx, z_ptr=d_zptr)
+        return net(x)
+
+    out_host = {}
+
+    def step_e2e():
+        f = h_feat.to(dev, non_blocking=True)
+        zi = h_zidx.to(dev, non_blocking=True)
+        zp = h_zptr.to(dev, non_blocking=True)
+        y = net(sphconv.SparseConvTensor(f, shape, B, z_idx=zi, z_ptr=zp))
+        for name, t in (("feature", y.feature), ("z_idx", y.z_idx), ("z_ptr", y.z_ptr)):
+            if name not in out_host or out_host[name].shape != t.shape:
+                out_host[name] = torch.empty(t.shape, dtype=t.dtype).pin_memory()
+            out_host[name].copy_(t, non_blocking=True)
+        return y
+
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)   # > 126 MB L2
+
+    def timed(fn, steps):
+        evs = []
+        for _ in range(steps):
+            flush.fill_(1.0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in evs]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with torch.no_grad():
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        t_wall0 = time.time()
+        for _ in range(args.warmup):
+            y = step_resident()
+        torch.cuda.synchronize()
+        sphconv.check_status()
+        out_rows = int(y.feature.shape[0])
+
+        # ---- resident-input timing (value), with per-layer sections for the roofline
+        barrier()
+        launches0 = lib.sph_kernel_launches()
+        profiling.enable(True)
+        times = timed(step_resident, args.steps)
+        sections = profiling.collect()
+        profiling.enable(False)
+        launches = (lib.sph_kernel_launches() - launches0) // args.steps
+        barrier()
+        total_ms = max_over_ranks(sum(times))
+
+        # ---- end to end from pinned host buffers
+        for _ in range(3):
+            step_e2e()
+        barrier()
+        e2e_times = timed(step_e2e, args.steps)
+        barrier()
+        e2e_total_ms = max_over_ranks(sum(e2e_times))
+        t_wall1 = time.time()
+        clocks = sampler.stop(t_wall0, t_wall1) if sampler is not None else None
+        sphconv.check_status()
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    scans = world * B * args.steps
+    value = scans / (total_ms * 1e-3)
+    e2e_value = scans / (e2e_total_ms * 1e-3)
+
+    # ---- per-layer accounting: algorithmic flops = 2*pairs*iC*oC, bytes = e*(rows_in*iC + rows_out*oC) + e*KV*iC*oC + 8*pairs
+    layers = {}
+    for name, ms, meta in sections:
+        ent = layers.setdefault(name, {"ms": 0.0, "n": 0, "meta": meta})
+        ent["ms"] += ms
+        ent["n"] += 1
+    layer_rows = []
+    tc_flops = tc_ms = 0.0
+    conv_ms = rules_ms = 0.0
+    pair_cache = {}
+    for name, ent in layers.items():
+        ms = ent["ms"] / ent["n"]
+        meta = ent["meta"]
+        if name.startswith("conv:"):
+            rules = meta["rules"]
+            tb = rules if not isinstance(rules, torch.Tensor) else rules._sph
+            key = id(tb)
+            if key not in pair_cache:
+                pair_cache[key] = int((tb.nbr >= 0).sum().item())
+            pairs = pair_cache[key]
+            iC, oC, e = meta["iC"], meta["oC"], meta["esize"]
+            flops = 2.0 * pairs * iC * oC
+            byts = e * (meta["n_in"] * iC + meta["n_out"] * oC) + e * 27 * iC * oC + 8.0 * pairs
+            tf = flops / (ms * 1e-3) / 1e12
+            gbs = byts / (ms * 1e-3) / 1e9
+            uses_tc = bool(lib.sph_conv_uses_tensor_cores(_capi.DTYPE_CODE[dtype], iC, oC))
+            layer_rows.append({"layer": name[5:], "ms": round(ms, 4), "pairs": pairs, "tflops": round(tf, 2),
+                               "gbs": round(gbs, 1), "frac_tensor": round(tf / peaks["tflops"], 4),
+                               "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "tensor_cores": uses_tc})
+            conv_ms += ms
+            if uses_tc:
+                tc_flops += flops
+                tc_ms += ms
+        else:
+            rules_ms += ms
+            layer_rows.append({"layer": name, "ms": round(ms, 4)})
+    achieved = tc_flops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
+    roofline = {"kernel": "conv_gather_tc_kernel (all tensor-core layers of one step)", "bound": "tensor",
+                "achieved": round(achieved, 2), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                "frac": round(achieved / peaks["tflops"], 4), "peak_source": "of " + peaks["source"] + " (burst bf16)",
+                "traffic": TRAFFIC_PER_STEP_BYTES.get((args.workload, B)),
+                "conv_ms_per_step": round(conv_ms, 4), "rules_ms_per_step": round(rules_ms, 4)}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        dt, _ = cpu_dense_scan(cfg, 0, threads)          # warm-up (thread pool, allocator)
+        dts = [cpu_dense_scan(cfg, 0, threads)[0] for _ in range(2)]
+        cpu = {"value": 1.0 / (sum(dts) / len(dts)), "unit": "scans/s", "cores": threads, "kind": "port",
+               "sample": "1 scan (B=1) of %s through all 8 layers as dense fp32 conv3d on the densified grid, mean of 2" % args.workload}
+
+    h2d = h_feat.numel() * h_feat.element_size() + h_zidx.numel() * 4 + h_zptr.numel() * 4
+    d2h = sum(t.numel() * t.element_size() for t in out_host.values())
+    line = {
+        "metric": "backbone scans/sec", "value": round(value, 2), "unit": "scans/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 4),
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
+        "config": {"workload": "%s: SECOND-style 8-layer encoder, %s inference, grid %s, %d scans per GPU per step"
+                               % (args.workload, dtype_name, "x".join(map(str, shape)), B),
+                   "scans_per_step": world * B, "out_rows_rank0": out_rows, "l2": "256 MB flush write between steps",
+                   "rule_sets_per_step": 5, "conv_layers_per_step": 8},
+        "e2e": {"value": round(e2e_value, 2), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_total_ms / args.steps, 4)},
+        "gpu_launches": int(launches) * args.steps,
+        "gpu_launches_per_step": int(launches),
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+        "clocks": clocks,
+        "layers": layer_rows,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of the tensor-core convolution launches of one step, from the ncu capture
+# summarised under profiles/; keyed by (workload, scans per GPU).  None until captured for that case.
+TRAFFIC_PER_STEP_BYTES = {}
+
+if __name__ == "__main__":
+    main()

@@ -54,6 +54,8 @@ typedef struct sph_geom {
 
 const char* sph_last_error(void);
 int sph_version(void);
+/* Kernels this library has launched so far in the process (all threads); for launch accounting in benchmarks. */
+int64_t sph_kernel_launches(void);
 
 /* ---- host-side geometry helpers --------------------------------------------------------------- */
 

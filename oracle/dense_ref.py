@@ -61,3 +61,25 @@ def dense_conv_grads(feature, weight5, d_out_dense_fn, z_idx, z_ptr, B, shape, s
     yd = torch.nn.functional.conv3d(dense, w, None, tuple(stride), tuple(padding))
     yd.backward(d_out_dense_fn(yd.detach()))
     return yd.detach(), f.grad, w.grad.permute(2, 3, 4, 1, 0).contiguous()
+
+
+def encoder_dense_forward(feature, z_idx, z_ptr, B, shape, layers, params, threads=None):
+    """Dense fp32 forward of a stack of 3x3x3 layers the way the reference's tests check single layers:
+    conv3d on the densified grid, submanifold outputs masked to the active sites, then bias + ReLU.
+    layers: [(subm, iC, oC, stride, key)], params: [(weight5, bias)].  Returns the dense output
+    [B, oC, o0, o1, o2] and the final occupancy mask."""
+    if threads:
+        torch.set_num_threads(threads)
+    x = densify(np.asarray(feature, dtype=np.float32), z_idx, z_ptr, B, shape)
+    mask = densify(np.ones((np.asarray(z_idx).shape[0], 1), np.float32), z_idx, z_ptr, B, shape) != 0
+    ones_w = torch.ones((1, 1, 3, 3, 3))
+    for (subm, iC, oC, stride, key), (w5, bias) in zip(layers, params):
+        w = torch.as_tensor(np.asarray(w5, dtype=np.float32)).permute(4, 3, 0, 1, 2).contiguous()
+        b = torch.as_tensor(np.asarray(bias, dtype=np.float32))
+        if subm:
+            x = torch.nn.functional.conv3d(x, w, None, 1, 1)
+        else:
+            x = torch.nn.functional.conv3d(x, w, None, stride, 1)
+            mask = torch.nn.functional.conv3d(mask.float(), ones_w, None, stride, 1) != 0
+        x = torch.relu(x + b.view(1, -1, 1, 1, 1)) * mask
+    return x, mask

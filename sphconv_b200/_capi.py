@@ -34,6 +34,7 @@ class Geom(ctypes.Structure):
 SIGNATURES = {
     "sph_last_error": (ctypes.c_char_p, []),
     "sph_version": (cint, []),
+    "sph_kernel_launches": (i64, []),
     "sph_out_spatial": (cint, [c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
     "sph_tile_n_max": (cint, [ctypes.POINTER(Geom), i64]),
     "sph_num_tiles": (cint, [ctypes.POINTER(Geom)]),

@@ -5,6 +5,7 @@ from typing import List, Optional
 import torch
 import torch.nn as nn
 
+from . import profiling
 from . import sphconv_cuda as ops
 from .functional import ConvFunction
 from .modules import SphModule
@@ -106,9 +107,11 @@ class Conv3d(Convolution):
         if not self.subm:
             out_shape = out_spatial(in_shape, self.kernel_size, self.stride, self.padding, self.dilation)
 
+        tag = self.name or "{}{}_{}".format("subm" if self.subm else "conv", in_channels, out_channels)
         datas = input.find_rule(self.indice_key) if self.indice_key is not None else None
         if datas is None:
-            datas = self._rules(input, in_shape, out_shape)
+            with profiling.section("rules:" + tag, subm=self.subm, n_in=input.feature.shape[0]):
+                datas = self._rules(input, in_shape, out_shape)
             if self.indice_key is not None:
                 input.rule_cache[self.indice_key] = datas
         oz_idx, oz_ptr, rules, rule_size, tile_grid_shape = datas
@@ -128,9 +131,11 @@ class Conv3d(Convolution):
                 out_feature = torch.relu(out_feature)
         else:
             weight = self._cached_packed(weight)
-            out_feature = ops.rule_conv(input.feature, weight, rules, rule_size, oz_idx.shape[0],
-                                        bias=None if bias is None else bias.detach().float(),
-                                        relu=self.activation == 'relu')
+            with profiling.section("conv:" + tag, iC=in_channels, oC=out_channels, n_in=input.feature.shape[0],
+                                   n_out=oz_idx.shape[0], rules=rules, esize=input.feature.element_size()):
+                out_feature = ops.rule_conv(input.feature, weight, rules, rule_size, oz_idx.shape[0],
+                                            bias=None if bias is None else bias.detach().float(),
+                                            relu=self.activation == 'relu')
         out_tensor = SparseConvTensor(out_feature, out_shape, batch_size, z_ptr=oz_ptr, z_idx=oz_idx)
         out_tensor.rule_cache = input.rule_cache
         return out_tensor

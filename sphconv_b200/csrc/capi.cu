@@ -2,11 +2,16 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace sph {
 
 static thread_local char g_err[512] = "";
+static std::atomic<long long> g_launches{0};
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -35,6 +40,7 @@ using namespace sph;
 
 extern "C" const char* sph_last_error(void) { return g_err; }
 extern "C" int sph_version(void) { return 100; }
+extern "C" int64_t sph_kernel_launches(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int64_t sph_packed_weight_bytes(int dtype, int32_t kv, int32_t k_ch, int32_t n_ch) {
   if (!conv_tc_supported(dtype, kv, k_ch, n_ch)) return 0;

@@ -12,6 +12,7 @@
 namespace sph {
 
 void set_error(const char* fmt, ...);
+void note_launch();  // counts kernels launched by this library (sph_kernel_launches)
 
 #define SPH_CHECK_ARG(cond, msg)                         \
   do {                                                   \
@@ -37,6 +38,7 @@ void set_error(const char* fmt, ...);
       ::sph::set_error("%s: kernel launch failed: %s", __func__, cudaGetErrorString(e__)); \
       return SPH_ERR_CUDA;                                                               \
     }                                                                                    \
+    ::sph::note_launch();                                                                \
   } while (0)
 
 __host__ __device__ inline int div_up(int a, int b) { return (a + b - 1) / b; }

@@ -26,7 +26,8 @@ def test_init_tensor_and_dense_roundtrip():
     idx = _coo(rng, B, shape, 0.3)
     feat = rng.standard_normal((idx.shape[0], C)).astype(np.float32)
     t = sphconv.SparseConvTensor(torch.as_tensor(feat, device=DEV), shape, B, indices=torch.as_tensor(idx, device=DEV))
-    assert t.shape == [B, C, *shape]
+    # the reference's shape property is [B, C, D, H, W] with (D, W, H) = (s0, s1, s2) (sphconv/tensor.py:104-106)
+    assert t.shape == [B, C, shape[0], shape[2], shape[1]]
     dense = t.dense().cpu()
     want = torch.zeros((B, C, *shape))
     want[idx[:, 0], :, idx[:, 1], idx[:, 2], idx[:, 3]] = torch.as_tensor(feat)
@@ -88,7 +89,7 @@ def test_sequential_rule_cache_and_dense_modules():
     with torch.no_grad():
         y = net(x)
     assert "subm0" in y.rule_cache and len(y.rule_cache) == 1
-    assert y.feature.shape[1] == 32 and y.shape[2:] == [4, 5, 6]
+    assert y.feature.shape[1] == 32 and [y.D, y.W, y.H] == [4, 5, 6]
     # dense reference of the same stack
     d = dense_ref.densify(feat.cpu().numpy(), z_idx, z_ptr, B, shape)
     mask = dense_ref.densify(np.ones((z_idx.shape[0], 1), np.float32), z_idx, z_ptr, B, shape) != 0
