@@ -245,6 +245,23 @@ def main():
         sphconv.check_status()
         out_rows = int(y.feature.shape[0])
 
+        # pairs per layer (for the algorithmic flop / byte counts), from one untimed step
+        profiling.enable(True)
+        profiling.capture_objects = True
+        step_resident()
+        pairs_of = {}
+        seen_tables = {}
+        for name, _, meta in profiling.collect():
+            if name.startswith("conv:"):
+                rules = meta["rules"]
+                tb = rules if not isinstance(rules, torch.Tensor) else rules._sph
+                if id(tb) not in seen_tables:
+                    seen_tables[id(tb)] = int((tb.nbr >= 0).sum().item())
+                pairs_of[name] = seen_tables[id(tb)]
+        profiling.capture_objects = False
+        profiling.enable(False)
+        del seen_tables, rules, tb, meta
+
         # ---- resident-input timing (value), with per-layer sections for the roofline
         barrier()
         launches0 = lib.sph_kernel_launches()
@@ -286,17 +303,11 @@ def main():
     layer_rows = []
     tc_flops = tc_ms = 0.0
     conv_ms = rules_ms = 0.0
-    pair_cache = {}
     for name, ent in layers.items():
         ms = ent["ms"] / ent["n"]
         meta = ent["meta"]
         if name.startswith("conv:"):
-            rules = meta["rules"]
-            tb = rules if not isinstance(rules, torch.Tensor) else rules._sph
-            key = id(tb)
-            if key not in pair_cache:
-                pair_cache[key] = int((tb.nbr >= 0).sum().item())
-            pairs = pair_cache[key]
+            pairs = pairs_of[name]
             iC, oC, e = meta["iC"], meta["oC"], meta["esize"]
             flops = 2.0 * pairs * iC * oC
             byts = e * (meta["n_in"] * iC + meta["n_out"] * oC) + e * 27 * iC * oC + 8.0 * pairs

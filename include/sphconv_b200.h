@@ -76,20 +76,23 @@ int sph_num_tiles(const sph_geom* g);
  *   d_rule_size  int32 [NTile, KV]                  (may be null together with d_rules)
  *   d_nbr        int32 [KV, nnz]: d_nbr[k][o] = input row paired with output row o at offset k, or -1 (may be null)
  *   fill_unused  != 0: entries of d_rules past rule_size are set to -1 as the reference does (rules.cu:364-366)
+ *   d_scratch    sph_rules_subm_scratch_bytes(g, nnz) bytes (0 for sparse inputs: then it may be null); holds a
+ *                per-column depth-bitmask index of the input, built when columns are long
  * The pair multiset of every (tile,k) list equals the reference's; the order inside a list is unspecified
  * there (atomics) and deterministic here. */
+int64_t sph_rules_subm_scratch_bytes(const sph_geom* g, int64_t nnz);
 int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
-                   int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int32_t* d_nbr,
+                   void* d_scratch, int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int32_t* d_nbr,
                    int fill_unused, int32_t* d_status, void* stream);
 
 /* Strided ("regular") sparse conv, step 1: output sparsity pattern.
  * ref: get_rules, src/sphconv/rules.cu:405-462 (prepareGridKernel + the cumsum/roll scans).
- *   d_scratch   sph_rules_strided_scratch_bytes(g) bytes; must be kept untouched until step 2 has run
+ *   d_scratch   sph_rules_strided_scratch_bytes(g, nnz) bytes; must be kept untouched until step 2 has run
  *   d_oz_ptr    int32 [B,oH,oW], inclusive prefix like z_ptr
  *   d_out_nnz   int32 [1] on the device (= oz_ptr[-1])
  *   h_out_nnz   optional host pointer: when non-null the call synchronises `stream` and stores the
  *               count there (the same device->host read the reference does at rules.cu:461) */
-int64_t sph_rules_strided_scratch_bytes(const sph_geom* g);
+int64_t sph_rules_strided_scratch_bytes(const sph_geom* g, int64_t nnz);
 int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
                             void* d_scratch, int32_t* d_oz_ptr, int32_t* d_out_nnz, int32_t* h_out_nnz,
                             void* stream);

@@ -30,7 +30,7 @@ constexpr int kTcThreads = 288;
 constexpr int kProducerThreads = 128;
 constexpr int kBlockRows = 128;
 constexpr int kMaxStages = 8;
-constexpr int kPrefetch = 4;       // neighbour-table entries kept in flight per producer lane
+constexpr int kPrefetch = 8;       // neighbour-table entries kept in flight per producer lane
 constexpr int kSmemBudget = 227 * 1024 - 2048;
 constexpr int kTcMaxKV = 64;
 
@@ -187,19 +187,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
 #pragma unroll
     for (int j = 0; j < kPrefetch; ++j) nb[j] = pf_load();
 
-    int k = 0;
+    int k = 0, s = 0;
+    uint32_t use = 0;
     bool bad = false;
-    for (int it = 0; it < total_iters; ++it) {
-      const int s = it % S;
-      const uint32_t use = (uint32_t)(it / S);
-      const int cur = nb[0];
-#pragma unroll
-      for (int j = 0; j + 1 < kPrefetch; ++j) nb[j] = nb[j + 1];
-      nb[kPrefetch - 1] = pf_load();
+    // One stage: wait for the slot, gather 128 rows for offset k, hand the slot over.  Returns true on abort.
+    auto fill_stage = [&](const int cur) -> bool {
       bad |= (cur == -2);
-
       mbar_wait(smem_u32(&s_empty[s]), (use & 1u) ^ 1u, abort_flag);
-      if (__any_sync(0xffffffffu, *abort_flag != 0)) break;  // warp-uniform: shuffles follow
+      if (__any_sync(0xffffffffu, *abort_flag != 0)) return true;  // warp-uniform: shuffles follow
       uint8_t* a_stage = stage0 + (size_t)s * stage_bytes;
       if (!p.w_resident && tid == 0) {
         mbar_arrive_expect_tx(smem_u32(&s_full[s]), (uint32_t)p.b_bytes);
@@ -224,6 +219,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       }
       cp_async_arrive_noinc(smem_u32(&s_full[s]));
       if (++k == p.kv) k = 0;
+      if (++s == S) { s = 0; ++use; }
+      return false;
+    };
+    // The ring is indexed with compile-time constants only: moving a register that is the destination of
+    // a load still in flight would stall on that load and serialise the whole pipeline.
+    bool stop = false;
+    for (int it0 = 0; it0 < total_iters && !stop; it0 += kPrefetch) {
+#pragma unroll
+      for (int j = 0; j < kPrefetch; ++j) {
+        if (it0 + j < total_iters && !stop) {
+          const int cur = nb[j];
+          nb[j] = pf_load();
+          stop = fill_stage(cur);
+        }
+      }
     }
     cp_async_wait_all();
     if (bad && p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
@@ -237,9 +247,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       const int n_mma = p.kc / 2;  // 32 bytes of K per instruction (16 x 16-bit or 32 x 8-bit)
       if (p.w_resident) mbar_wait(smem_u32(&s_w_full), 0u, abort_flag);
       int k = 0, blk_i = 0;
+      int s = 0;
+      uint32_t use = 0;
       for (int it = 0; it < total_iters; ++it) {
-        const int s = it % S;
-        const uint32_t use = (uint32_t)(it / S);
         const int buf = blk_i & 1;
         if (k == 0) {
           mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)blk_i >> 1) & 1u) ^ 1u, abort_flag);
@@ -259,6 +269,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
           else umma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
         }
         umma_commit(smem_u32(&s_empty[s]));
+        if (++s == S) { s = 0; ++use; }
         if (++k == p.kv) {
           umma_commit(smem_u32(&s_acc_full[buf]));
           k = 0;

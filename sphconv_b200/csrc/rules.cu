@@ -22,15 +22,32 @@ constexpr int kEmitThreads = kEmitWarps * 32;
 constexpr int kEmitCap = 1024;      // output voxels staged per pass
 constexpr int kEmitMaxRanges = 128; // (batch, tile row) ranges handled per group
 constexpr int kMaxKV = 343;         // 7x7x7
+constexpr int kMaxKD = 7;           // kernel extent along depth
 
 __device__ __forceinline__ int col_start(const int* __restrict__ zp, int64_t c) {
   return c == 0 ? 0 : __ldg(zp + c - 1);
 }
 
-// Row id of input voxel (b,ix,iy,iz) or -1.  Columns hold a handful of entries, so a linear scan wins.
+// Per-column depth bitmask of the INPUT tensor, used when columns are long: word w of column c holds
+// {bits of depths [32w, 32w+32), number of set bits in the words before w}.  "Is depth iz active, and which
+// row is it" is then one 8-byte load plus the column start - valid only when every column is stored in
+// ascending depth order, which the table's builder checks (flag != 0 means some column is not).
+struct ColMask {
+  const uint2* table;  // null: not built (short columns), scan the column instead
+  int words;
+  const int* unsorted;  // device flag written by the builder
+};
+
+// Row id of input voxel (b,ix,iy,iz) or -1.
 __device__ __forceinline__ int find_row(const int* __restrict__ zi, const int* __restrict__ zp, const Geom& g,
-                                        int b, int ix, int iy, int iz) {
+                                        const ColMask& cm, bool use_mask, int b, int ix, int iy, int iz) {
   int64_t c = ((int64_t)b * g.H + ix) * g.W + iy;
+  if (use_mask) {
+    uint2 e = __ldg(cm.table + c * cm.words + (iz >> 5));
+    uint32_t bit = 1u << (iz & 31);
+    if (!(e.x & bit)) return -1;
+    return col_start(zp, c) + (int)e.y + __popc(e.x & (bit - 1u));
+  }
   int s = col_start(zp, c);
   int e = __ldg(zp + c);
   for (int r = s; r < e; ++r) {
@@ -39,13 +56,39 @@ __device__ __forceinline__ int find_row(const int* __restrict__ zi, const int* _
   return -1;
 }
 
+// One thread per input column: set the depth bits, then the running popcount.  The table must be zeroed.
+__global__ void __launch_bounds__(256)
+build_colmask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, int64_t ncols, int words, int D,
+                     uint2* __restrict__ table, int* __restrict__ unsorted) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ncols) return;
+  const int s = col_start(zp, c), e = __ldg(zp + c);
+  if (e <= s) return;
+  uint2* row = table + c * words;
+  int prev = -1;
+  bool bad = false;
+  for (int r = s; r < e; ++r) {
+    int z = __ldg(zi + r);
+    if (z <= prev || z >= D) bad = true;
+    prev = z;
+    if (z >= 0 && z < D) row[z >> 5].x |= 1u << (z & 31);
+  }
+  if (bad) *unsorted = 1;
+  uint32_t run = 0;
+  for (int w = 0; w < words; ++w) {
+    uint32_t bits = row[w].x;
+    row[w].y = run;
+    run += __popc(bits);
+  }
+}
+
 // One CTA per output tile.  in_* describe the input tensor, out_* the output tensor (the same
 // arrays for a submanifold layer).
 __global__ void __launch_bounds__(kEmitThreads)
 emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, const int* __restrict__ out_zi,
                   const int* __restrict__ out_zp, Geom g, int64_t in_nnz, int64_t out_nnz, int tile_n_max,
                   int* __restrict__ rules, int* __restrict__ rule_size, int* __restrict__ nbr,
-                  int* __restrict__ nbr_t, int* __restrict__ status) {
+                  int* __restrict__ nbr_t, ColMask cm, int* __restrict__ status) {
   __shared__ int s_cnt[kMaxKV];
   __shared__ int s_rstart[kEmitMaxRanges];
   __shared__ int s_roff[kEmitMaxRanges + 1];
@@ -63,6 +106,7 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
   const int tHe = min(g.tH, g.oH - ox0);
   const int tWe = min(g.tW, g.oW - oy0);
   const int R = g.B * tHe;  // (batch, tile row) ranges; each is one contiguous run of output rows
+  const bool use_mask = cm.table != nullptr && *cm.unsorted == 0;
 
   for (int k = tid; k < g.KV; k += kEmitThreads) s_cnt[k] = 0;
   __syncthreads();
@@ -109,42 +153,88 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
       }
       __syncthreads();
 
-      // ---- one warp per kernel offset
-      for (int k = warp; k < g.KV; k += kEmitWarps) {
-        const int kh = k / (g.KW * g.KD), kw = (k / g.KD) % g.KW, kd = k % g.KD;
-        int base = s_cnt[k];
-        int* lst_in = rules ? rules + ((int64_t)t * g.KV + k) * 2 * tile_n_max : nullptr;
-        int* lst_out = rules ? lst_in + tile_n_max : nullptr;
+      // ---- one warp per (kh,kw): the KD offsets along depth read the same input column, so one look at
+      //      that column serves all of them
+      for (int kk = warp; kk < g.KH * g.KW; kk += kEmitWarps) {
+        const int kh = kk / g.KW, kw = kk % g.KW;
+        const int k0 = kk * g.KD;
+        int base[kMaxKD];
+#pragma unroll
+        for (int j = 0; j < kMaxKD; ++j) base[j] = j < g.KD ? s_cnt[k0 + j] : 0;
         for (int c = 0; c < np; c += 32) {
           const int v = c + lane;
-          int in_row = -1, out_row = -1;
+          int found[kMaxKD];
+#pragma unroll
+          for (int j = 0; j < kMaxKD; ++j) found[j] = -1;
+          int out_row = -1;
           if (v < np) {
             out_row = s_vrow[v];
-            int b = s_vb[v];
-            unsigned xy = s_vxy[v];
-            int ix = (int)(xy >> 16) * g.sH - g.pH + kh;
-            int iy = (int)(xy & 0xffffu) * g.sW - g.pW + kw;
-            int iz = s_voz[v] * g.sD - g.pD + kd;
-            if (ix >= 0 && ix < g.H && iy >= 0 && iy < g.W && iz >= 0 && iz < g.D)
-              in_row = find_row(in_zi, in_zp, g, b, ix, iy, iz);
-            if (nbr) nbr[(int64_t)k * out_nnz + out_row] = in_row;
-          }
-          unsigned m = __ballot_sync(0xffffffffu, in_row >= 0);
-          if (in_row >= 0) {
-            int slot = base + __popc(m & ((1u << lane) - 1u));
-            if (lst_in) {
-              if (slot < tile_n_max) {
-                lst_in[slot] = in_row;
-                lst_out[slot] = out_row;
-              } else if (status) {
-                atomicOr(status, SPH_STATUS_RULE_OVERFLOW);
+            const int b = s_vb[v];
+            const unsigned xy = s_vxy[v];
+            const int ix = (int)(xy >> 16) * g.sH - g.pH + kh;
+            const int iy = (int)(xy & 0xffffu) * g.sW - g.pW + kw;
+            const int iz0 = s_voz[v] * g.sD - g.pD;   // input depth for kd = 0; kd = j reads iz0 + j
+            if (ix >= 0 && ix < g.H && iy >= 0 && iy < g.W) {
+              const int64_t ci = ((int64_t)b * g.H + ix) * g.W + iy;
+              if (use_mask) {
+                int cur_w = -1;
+                uint2 e = make_uint2(0u, 0u);
+                int cstart = -1;
+#pragma unroll
+                for (int j = 0; j < kMaxKD; ++j) {
+                  const int iz = iz0 + j;
+                  if (j < g.KD && iz >= 0 && iz < g.D) {
+                    if ((iz >> 5) != cur_w) {
+                      cur_w = iz >> 5;
+                      e = __ldg(cm.table + ci * cm.words + cur_w);
+                    }
+                    const uint32_t bit = 1u << (iz & 31);
+                    if (e.x & bit) {
+                      if (cstart < 0) cstart = col_start(in_zp, ci);
+                      found[j] = cstart + (int)e.y + __popc(e.x & (bit - 1u));
+                    }
+                  }
+                }
+              } else {
+                const int cs = col_start(in_zp, ci), ce = __ldg(in_zp + ci);
+                for (int r = cs; r < ce; ++r) {
+                  const int d = __ldg(in_zi + r) - iz0;
+#pragma unroll
+                  for (int j = 0; j < kMaxKD; ++j)
+                    if (d == j && j < g.KD && found[j] < 0) found[j] = r;
+                }
               }
             }
-            if (nbr_t) nbr_t[(int64_t)k * in_nnz + in_row] = out_row;
           }
-          base += __popc(m);
+#pragma unroll
+          for (int j = 0; j < kMaxKD; ++j) {
+            if (j < g.KD) {   // uniform across the warp
+              const int k = k0 + j;
+              const int in_row = found[j];
+              if (v < np && nbr) nbr[(int64_t)k * out_nnz + out_row] = in_row;
+              const unsigned m = __ballot_sync(0xffffffffu, in_row >= 0);
+              if (in_row >= 0) {
+                const int slot = base[j] + __popc(m & ((1u << lane) - 1u));
+                if (rules) {
+                  int* lst_in = rules + ((int64_t)t * g.KV + k) * 2 * tile_n_max;
+                  if (slot < tile_n_max) {
+                    lst_in[slot] = in_row;
+                    lst_in[tile_n_max + slot] = out_row;
+                  } else if (status) {
+                    atomicOr(status, SPH_STATUS_RULE_OVERFLOW);
+                  }
+                }
+                if (nbr_t) nbr_t[(int64_t)k * in_nnz + in_row] = out_row;
+              }
+              base[j] += __popc(m);
+            }
+          }
         }
-        if (lane == 0) s_cnt[k] = base;
+        if (lane == 0) {
+#pragma unroll
+          for (int j = 0; j < kMaxKD; ++j)
+            if (j < g.KD) s_cnt[k0 + j] = base[j];
+        }
       }
       __syncthreads();
     }
@@ -188,16 +278,34 @@ __device__ __forceinline__ int block_inclusive_scan(int v, int* s_warp /*[8]*/, 
 
 __global__ void __launch_bounds__(kScanThreads)
 strided_mask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, Geom g, int words, int64_t ncols,
-                    uint32_t* __restrict__ mask, int* __restrict__ counts, int* __restrict__ blocksum) {
+                    ColMask cm, uint32_t* __restrict__ mask, int* __restrict__ counts, int* __restrict__ blocksum) {
   __shared__ int s_warp[kScanThreads / 32];
   const int64_t c = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
+  const bool use_mask = cm.table != nullptr && *cm.unsorted == 0;
   int count = 0;
   if (c < ncols) {
     const int oy = (int)(c % g.oW);
     const int ox = (int)((c / g.oW) % g.oH);
     const int b = (int)(c / ((int64_t)g.oW * g.oH));
-    for (int w = 0; w < words; ++w) {
-      uint32_t m = 0;
+    for (int w0 = 0; w0 < words; w0 += 8) {   // 8 output words (256 depth bins) per pass
+      uint32_t m[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m[j] = 0;
+      auto add_depth = [&](int z) {
+        for (int kd = 0; kd < g.KD; ++kd) {
+          int num = z + g.pD - kd;
+          if (num < 0) break;
+          if (num % g.sD) continue;
+          int oz = num / g.sD;
+          int wi = (oz >> 5) - w0;
+          if (oz < g.oD && wi >= 0 && wi < 8) {
+            uint32_t bit = 1u << (oz & 31);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (wi == j) m[j] |= bit;
+          }
+        }
+      };
       for (int kh = 0; kh < g.KH; ++kh) {
         int ix = ox * g.sH - g.pH + kh;
         if (ix < 0 || ix >= g.H) continue;
@@ -205,21 +313,28 @@ strided_mask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, Geom
           int iy = oy * g.sW - g.pW + kw;
           if (iy < 0 || iy >= g.W) continue;
           int64_t ci = ((int64_t)b * g.H + ix) * g.W + iy;
-          int s = col_start(zp, ci), e = __ldg(zp + ci);
-          for (int r = s; r < e; ++r) {
-            int z = __ldg(zi + r);
-            for (int kd = 0; kd < g.KD; ++kd) {
-              int num = z + g.pD - kd;
-              if (num < 0) break;
-              if (num % g.sD) continue;
-              int oz = num / g.sD;
-              if (oz < g.oD && (oz >> 5) == w) m |= 1u << (oz & 31);
+          if (use_mask) {
+            for (int w = 0; w < cm.words; ++w) {
+              uint32_t bits = __ldg(cm.table + ci * cm.words + w).x;
+              while (bits) {
+                int z = w * 32 + __ffs(bits) - 1;
+                bits &= bits - 1;
+                add_depth(z);
+              }
             }
+          } else {
+            int s = col_start(zp, ci), e = __ldg(zp + ci);
+            for (int r = s; r < e; ++r) add_depth(__ldg(zi + r));
           }
         }
       }
-      mask[c * words + w] = m;
-      count += __popc(m);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (w0 + j < words) {
+          mask[c * words + w0 + j] = m[j];
+          count += __popc(m[j]);
+        }
+      }
     }
     counts[c] = count;
   }
@@ -296,9 +411,37 @@ __global__ void rules_to_nbr_kernel(const int* __restrict__ rules, const int* __
   }
 }
 
+// Input column masks pay off once columns hold more than a couple of voxels (deeper encoder levels).
+bool want_colmask(const Geom& g, int64_t in_nnz) { return in_nnz > 2 * (int64_t)g.B * g.H * g.W; }
+
+size_t colmask_bytes(const Geom& g, int64_t in_nnz) {
+  if (!want_colmask(g, in_nnz)) return 0;
+  size_t b = 256 + (size_t)g.B * g.H * g.W * div_up(g.D, 32) * sizeof(uint2);
+  return (b + 255) & ~(size_t)255;
+}
+
+// Builds the table at `scratch` (layout: 256-byte header holding the unsorted flag, then the table).
+int build_colmask(const int* zi, const int* zp, const Geom& g, int64_t in_nnz, void* scratch, ColMask* cm,
+                  cudaStream_t st) {
+  cm->table = nullptr;
+  cm->words = 0;
+  cm->unsorted = nullptr;
+  if (!want_colmask(g, in_nnz) || scratch == nullptr) return SPH_OK;
+  const int64_t ncols = (int64_t)g.B * g.H * g.W;
+  const int words = div_up(g.D, 32);
+  SPH_CUDA(cudaMemsetAsync(scratch, 0, colmask_bytes(g, in_nnz), st));
+  cm->unsorted = (const int*)scratch;
+  cm->words = words;
+  cm->table = (const uint2*)((char*)scratch + 256);
+  build_colmask_kernel<<<(unsigned)div_up64(ncols, 256), 256, 0, st>>>(zi, zp, ncols, words, g.D,
+                                                                        (uint2*)((char*)scratch + 256), (int*)scratch);
+  SPH_LAUNCH_CHECK();
+  return SPH_OK;
+}
+
 int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int* out_zp, const Geom& g,
                 int64_t in_nnz, int64_t out_nnz, int tnm, int* rules, int* rule_size, int* nbr, int* nbr_t,
-                int fill_unused, int* status, cudaStream_t st) {
+                const ColMask& cm, int fill_unused, int* status, cudaStream_t st) {
   if (rules && fill_unused) {
     SPH_CUDA(cudaMemsetAsync(rules, 0xFF, (size_t)g.nTile * g.KV * 2 * (size_t)tnm * sizeof(int), st));
   }
@@ -306,7 +449,7 @@ int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int
     SPH_CUDA(cudaMemsetAsync(nbr_t, 0xFF, (size_t)g.KV * (size_t)in_nnz * sizeof(int), st));
   }
   emit_rules_kernel<<<g.nTile, kEmitThreads, 0, st>>>(in_zi, in_zp, out_zi, out_zp, g, in_nnz, out_nnz, tnm, rules,
-                                                      rule_size, nbr, nbr_t, status);
+                                                      rule_size, nbr, nbr_t, cm, status);
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
@@ -332,6 +475,10 @@ int make_geom(const sph_geom* s, Geom* o) {
   g.KV = g.KH * g.KW * g.KD;
   if (g.KV > kMaxKV) {
     set_error("kernel volume %d exceeds the maximum %d", g.KV, kMaxKV);
+    return SPH_ERR_LIMIT;
+  }
+  if (g.KD > kMaxKD) {
+    set_error("kernel depth %d exceeds the maximum %d", g.KD, kMaxKD);
     return SPH_ERR_LIMIT;
   }
   if (g.oH > 65535 || g.oW > 65535) {
@@ -386,9 +533,16 @@ extern "C" int sph_tile_n_max(const sph_geom* s, int64_t nnz) {
   return (int)(size + 64) & (-1 << 4);
 }
 
+extern "C" int64_t sph_rules_subm_scratch_bytes(const sph_geom* s, int64_t nnz) {
+  Geom g;
+  int rc = make_geom(s, &g);
+  if (rc != SPH_OK) return rc;
+  return (int64_t)colmask_bytes(g, nnz);
+}
+
 extern "C" int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* s,
-                              int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int32_t* d_nbr,
-                              int fill_unused, int32_t* d_status, void* stream) {
+                              void* d_scratch, int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size,
+                              int32_t* d_nbr, int fill_unused, int32_t* d_status, void* stream) {
   Geom g;
   int rc = make_geom(s, &g);
   if (rc != SPH_OK) return rc;
@@ -396,8 +550,11 @@ extern "C" int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, in
   SPH_CHECK_ARG(g.H == g.oH && g.W == g.oW && g.D == g.oD, "submanifold rules need out_shape == in_shape");
   SPH_CHECK_ARG((d_rules == nullptr) == (d_rule_size == nullptr), "rules and rule_size go together");
   SPH_CHECK_ARG(d_rules == nullptr || tile_n_max > 0, "tile_n_max must be positive");
+  ColMask cm;
+  rc = build_colmask(d_z_idx, d_z_ptr, g, nnz, d_scratch, &cm, (cudaStream_t)stream);
+  if (rc != SPH_OK) return rc;
   return launch_emit(d_z_idx, d_z_ptr, d_z_idx, d_z_ptr, g, nnz, nnz, tile_n_max, d_rules, d_rule_size, d_nbr,
-                     nullptr, fill_unused, d_status, (cudaStream_t)stream);
+                     nullptr, cm, fill_unused, d_status, (cudaStream_t)stream);
 }
 
 namespace {
@@ -405,25 +562,40 @@ struct StridedScratch {
   int words;
   int64_t ncols;
   int nblk;
-  size_t mask_bytes, blocksum_bytes;
+  size_t mask_bytes, blocksum_bytes, colmask_bytes;
 };
-StridedScratch strided_layout(const Geom& g) {
+StridedScratch strided_layout(const Geom& g, int64_t nnz) {
   StridedScratch s;
   s.words = div_up(g.oD, 32);
   s.ncols = (int64_t)g.B * g.oH * g.oW;
   s.nblk = (int)div_up64(s.ncols, kScanThreads);
   s.mask_bytes = ((size_t)s.ncols * s.words * sizeof(uint32_t) + 255) & ~(size_t)255;
   s.blocksum_bytes = ((size_t)s.nblk * sizeof(int) + 255) & ~(size_t)255;
+  s.colmask_bytes = colmask_bytes(g, nnz);
   return s;
+}
+// The input column-mask table sits behind the output masks and block sums; step 1 builds it, step 2 reuses it.
+ColMask strided_colmask(const Geom& g, int64_t nnz, const StridedScratch& l, const void* scratch) {
+  ColMask cm;
+  cm.table = nullptr;
+  cm.words = 0;
+  cm.unsorted = nullptr;
+  if (l.colmask_bytes) {
+    const char* base = (const char*)scratch + l.mask_bytes + l.blocksum_bytes;
+    cm.unsorted = (const int*)base;
+    cm.words = div_up(g.D, 32);
+    cm.table = (const uint2*)(base + 256);
+  }
+  return cm;
 }
 }  // namespace
 
-extern "C" int64_t sph_rules_strided_scratch_bytes(const sph_geom* s) {
+extern "C" int64_t sph_rules_strided_scratch_bytes(const sph_geom* s, int64_t nnz) {
   Geom g;
   int rc = make_geom(s, &g);
   if (rc != SPH_OK) return rc;
-  StridedScratch l = strided_layout(g);
-  return (int64_t)(l.mask_bytes + l.blocksum_bytes);
+  StridedScratch l = strided_layout(g, nnz);
+  return (int64_t)(l.mask_bytes + l.blocksum_bytes + l.colmask_bytes);
 }
 
 extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz,
@@ -434,10 +606,14 @@ extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_
   if (rc != SPH_OK) return rc;
   SPH_CHECK_ARG(d_z_ptr && d_scratch && d_oz_ptr && d_out_nnz && (nnz == 0 || d_z_idx), "null argument");
   cudaStream_t st = (cudaStream_t)stream;
-  StridedScratch l = strided_layout(g);
+  StridedScratch l = strided_layout(g, nnz);
   uint32_t* mask = (uint32_t*)d_scratch;
   int* blocksum = (int*)((char*)d_scratch + l.mask_bytes);
-  strided_mask_kernel<<<l.nblk, kScanThreads, 0, st>>>(d_z_idx, d_z_ptr, g, l.words, l.ncols, mask, d_oz_ptr,
+  ColMask cm;
+  rc = build_colmask(d_z_idx, d_z_ptr, g, nnz, l.colmask_bytes ? (char*)d_scratch + l.mask_bytes + l.blocksum_bytes : nullptr,
+                     &cm, st);
+  if (rc != SPH_OK) return rc;
+  strided_mask_kernel<<<l.nblk, kScanThreads, 0, st>>>(d_z_idx, d_z_ptr, g, l.words, l.ncols, cm, mask, d_oz_ptr,
                                                        blocksum);
   SPH_LAUNCH_CHECK();
   scan_blocksums_kernel<<<1, kScanThreads, 0, st>>>(blocksum, l.nblk, d_out_nnz);
@@ -464,14 +640,14 @@ extern "C" int sph_rules_strided_fill(const int32_t* d_z_idx, const int32_t* d_z
   SPH_CHECK_ARG((d_rules == nullptr) == (d_rule_size == nullptr), "rules and rule_size go together");
   SPH_CHECK_ARG(d_rules == nullptr || tile_n_max > 0, "tile_n_max must be positive");
   cudaStream_t st = (cudaStream_t)stream;
-  StridedScratch l = strided_layout(g);
+  StridedScratch l = strided_layout(g, nnz);
   const uint32_t* mask = (const uint32_t*)d_scratch;
   if (out_nnz > 0) {
     write_oz_idx_kernel<<<l.nblk, kScanThreads, 0, st>>>(mask, d_oz_ptr, l.words, l.ncols, d_oz_idx);
     SPH_LAUNCH_CHECK();
   }
   return launch_emit(d_z_idx, d_z_ptr, d_oz_idx, d_oz_ptr, g, nnz, out_nnz, tile_n_max, d_rules, d_rule_size,
-                     d_nbr, d_nbr_t, fill_unused, d_status, st);
+                     d_nbr, d_nbr_t, strided_colmask(g, nnz, l, d_scratch), fill_unused, d_status, st);
 }
 
 extern "C" int sph_rules_to_nbr(const int32_t* d_rules, const int32_t* d_rule_size, int32_t n_tile, int32_t kv,

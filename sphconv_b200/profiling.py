@@ -4,6 +4,7 @@ import contextlib
 import torch
 
 _active = False
+capture_objects = False   # sections may attach tensors to their meta only while this is set (they stay alive until collect)
 _records = []   # (name, start_event, stop_event, meta)
 
 

@@ -70,8 +70,10 @@ def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, s
         rules = torch.empty((n_tile, kv, 2, tnm), dtype=torch.int32, device=dev)
         rule_size = torch.empty((n_tile, kv), dtype=torch.int32, device=dev)
     nbr = torch.empty((kv, nnz), dtype=torch.int32, device=dev)
+    scratch_bytes = C.check(lib.sph_rules_subm_scratch_bytes(ctypes.byref(g), nnz))
+    scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=dev) if scratch_bytes else None
     with torch.cuda.device(dev):
-        C.check(lib.sph_rules_subm(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), tnm, C.ptr(rules),
+        C.check(lib.sph_rules_subm(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), C.ptr(scratch), tnm, C.ptr(rules),
                                    C.ptr(rule_size), C.ptr(nbr), int(config.fill_unused_rules),
                                    C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
     symmetric = all(int(k) % 2 == 1 and int(p) == int(k) // 2 and int(s) == 1
@@ -94,7 +96,7 @@ def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatia
     g = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
     kv = int(kernelSize[0]) * int(kernelSize[1]) * int(kernelSize[2])
     n_tile = C.check(lib.sph_num_tiles(ctypes.byref(g)))
-    scratch_bytes = C.check(lib.sph_rules_strided_scratch_bytes(ctypes.byref(g)))
+    scratch_bytes = C.check(lib.sph_rules_strided_scratch_bytes(ctypes.byref(g), nnz))
     scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=dev)
     oz_ptr = torch.empty((batchSize, int(outSpatialShape[0]), int(outSpatialShape[1])), dtype=torch.int32, device=dev)
     d_count = torch.empty((1,), dtype=torch.int32, device=dev)
