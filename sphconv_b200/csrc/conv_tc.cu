@@ -17,6 +17,8 @@
 //
 // Shared-memory operand layout (no swizzle): 8-row x 16-byte core matrices of 128 contiguous bytes;
 // A: core (row group g, chunk c) at c*2048 + g*128; B: core (channel group gn, chunk c) at c*(N/8)*128 + gn*128.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -26,13 +28,12 @@ namespace {
 
 using namespace tc;
 
+constexpr int kTcMaxKV = 32;       // kernel volume the tensor-core kernel handles (3x3x3 = 27)
 constexpr int kTcThreads = 288;
 constexpr int kProducerThreads = 128;
 constexpr int kBlockRows = 128;
 constexpr int kMaxStages = 8;
-constexpr int kPrefetch = 8;       // neighbour-table entries kept in flight per producer lane
-constexpr int kSmemBudget = 227 * 1024 - 2048;
-constexpr int kTcMaxKV = 64;
+constexpr int kSmemBudget = 227 * 1024 - 2048 - 4 * kTcMaxKV * 32 * 4;   // minus barriers and the table buffer
 
 struct TcParams {
   const void* rows;
@@ -55,6 +56,7 @@ struct TcParams {
   int* status;
   int tmem_cols;
   int num_blocks;
+  int gk;               // kernel offsets gathered per pipeline stage
 };
 
 __device__ __forceinline__ void store16(void* out, int out_dtype, int64_t elem_idx, const float (&v)[16]) {
@@ -115,14 +117,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   __shared__ __align__(8) uint64_t s_w_full;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ int s_tbl[4][kTcMaxKV][32];   // per producer warp: neighbour-table entries of the current row block
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int S = p.stages;
-  const int stage_bytes = p.a_bytes + (p.w_resident ? 0 : p.b_bytes);
-  uint8_t* w_smem = smem;                                        // resident weights (if any)
+  const int GK = p.gk;                                             // kernel offsets per pipeline stage
+  const int stage_bytes = GK * (p.a_bytes + (p.w_resident ? 0 : p.b_bytes));
+  uint8_t* w_smem = smem;                                          // resident weights (if any)
   uint8_t* stage0 = smem + (p.w_resident ? p.kv * p.b_bytes : 0);  // multiple of 128 bytes either way
+  const int groups = (p.kv + GK - 1) / GK;                         // stages per row block
 
   if (tid == 0) {
     s_abort = 0;
@@ -149,10 +154,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
 
   // blocks handled by this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
   const int my_blocks = (p.num_blocks - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int total_iters = my_blocks * p.kv;
 
   if (warp < 4) {
     // ======================= gather producers =======================
+    // Lane <-> output row (32*warp + lane of the block).  The per-stage instruction stream of a producer
+    // warp is the pipeline's critical path, so it is kept to: one barrier poll, one shared-memory read
+    // of the neighbour row id, kc 16-byte cp.async per offset, one arrive.  The neighbour-table entries
+    // of the NEXT block are loaded into registers while the current block is gathered and parked in
+    // shared memory at the block boundary, so no global-load latency sits on that path.
     if (p.w_resident && tid == 0) {
       const uint32_t bytes = (uint32_t)(p.kv * p.b_bytes);
       mbar_arrive_expect_tx(smem_u32(&s_w_full), bytes);
@@ -161,79 +170,57 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
         bulk_g2s(smem_u32(w_smem + (size_t)k * p.b_bytes), (const uint8_t*)p.packed + (size_t)k * p.b_bytes,
                  (uint32_t)p.b_bytes, smem_u32(&s_w_full));
     }
-    // chunk / row-group assignment of this lane inside one cp.async instruction
-    const int cpi = p.kc < 4 ? p.kc : 4;     // chunks covered per instruction (kc is 2, 4, 8, ...)
-    const int gpi = 4 / cpi;                 // 8-row groups covered per instruction
-    const int l_row = lane & 7;
-    const int l_chunk = (lane >> 3) % cpi;
-    const int l_grp = (lane >> 3) / cpi;
     const uint8_t* rows = (const uint8_t*)p.rows;
-
-    // neighbour-table prefetch ring: entry j belongs to iteration it + j, lane <-> row 32*warp + lane
-    int nb[kPrefetch];
-    int pf_blk = blockIdx.x, pf_k = 0, pf_it = 0;
-    auto pf_load = [&]() -> int {
-      int v = -1;
-      if (pf_it < total_iters) {
-        int64_t r = (int64_t)pf_blk * kBlockRows + warp * 32 + lane;
-        int tk = p.flip_k ? p.kv - 1 - pf_k : pf_k;
-        if (r < p.n_out) v = __ldg(p.nbr + (int64_t)tk * p.n_out + r);
-        if (v >= p.n_rows) v = -2;
-      }
-      ++pf_it;
-      if (++pf_k == p.kv) { pf_k = 0; pf_blk += gridDim.x; }
-      return v;
-    };
+    int* tbl = &s_tbl[warp][0][lane];   // entry of offset k at tbl[k * 32]
+    int tmp[kTcMaxKV];
+    auto load_table = [&](int blk) {
+      const int64_t r = (int64_t)blk * kBlockRows + warp * 32 + lane;
 #pragma unroll
-    for (int j = 0; j < kPrefetch; ++j) nb[j] = pf_load();
+      for (int k = 0; k < kTcMaxKV; ++k) {
+        if (k < p.kv) {
+          const int tk = p.flip_k ? p.kv - 1 - k : k;
+          tmp[k] = r < p.n_out ? __ldg(p.nbr + (int64_t)tk * p.n_out + r) : -1;
+        }
+      }
+    };
+    auto park_table = [&]() {
+#pragma unroll
+      for (int k = 0; k < kTcMaxKV; ++k)
+        if (k < p.kv) tbl[k * 32] = tmp[k];
+    };
+    load_table((int)blockIdx.x);
+    park_table();
 
-    int k = 0, s = 0;
+    int s = 0;
     uint32_t use = 0;
-    bool bad = false;
-    // One stage: wait for the slot, gather 128 rows for offset k, hand the slot over.  Returns true on abort.
-    auto fill_stage = [&](const int cur) -> bool {
-      bad |= (cur == -2);
-      mbar_wait(smem_u32(&s_empty[s]), (use & 1u) ^ 1u, abort_flag);
-      if (__any_sync(0xffffffffu, *abort_flag != 0)) return true;  // warp-uniform: shuffles follow
-      uint8_t* a_stage = stage0 + (size_t)s * stage_bytes;
-      if (!p.w_resident && tid == 0) {
-        mbar_arrive_expect_tx(smem_u32(&s_full[s]), (uint32_t)p.b_bytes);
-        bulk_g2s(smem_u32(a_stage + p.a_bytes), (const uint8_t*)p.packed + (size_t)k * p.b_bytes, (uint32_t)p.b_bytes,
-                 smem_u32(&s_full[s]));
-      }
-      // rows 32*warp .. 32*warp+31 = row groups 4*warp .. 4*warp+3
-      for (int gq = 0; gq < 4; gq += gpi) {
-        const int g_local = gq + l_grp;                       // 0..3
-        const int src_lane = g_local * 8 + l_row;             // lane holding this row's table entry
-        const int in_row = __shfl_sync(0xffffffffu, cur, src_lane);
-        const int g = warp * 4 + g_local;
-        const uint32_t ok = in_row >= 0 ? 16u : 0u;
-        const uint8_t* src_row = rows + (size_t)(in_row >= 0 ? in_row : 0) * p.row_bytes;
-        for (int c0 = 0; c0 < p.kc; c0 += cpi) {
-          const int c = c0 + l_chunk;
-          if (c < p.kc) {
-            const uint32_t dst = smem_u32(a_stage) + (uint32_t)(c * 2048 + g * 128 + l_row * 16);
-            cp_async_16(dst, src_row + c * 16, ok);
-          }
+    bool bad = false, dead = false;
+    const uint32_t row_off = (uint32_t)((warp * 32 + lane) * 16);
+    for (int bi = 0; bi < my_blocks && !dead; ++bi) {
+      const bool has_next = bi + 1 < my_blocks;
+      if (has_next) load_table((int)blockIdx.x + (bi + 1) * (int)gridDim.x);
+      for (int grp = 0; grp < groups; ++grp) {
+        if (!mbar_wait(smem_u32(&s_empty[s]), (use & 1u) ^ 1u, abort_flag)) { dead = true; break; }
+        uint8_t* stage = stage0 + (size_t)s * stage_bytes;
+        const int k0 = grp * GK;
+        const int nk = min(GK, p.kv - k0);
+        if (!p.w_resident && tid == 0) {
+          const uint32_t bytes = (uint32_t)(nk * p.b_bytes);
+          mbar_arrive_expect_tx(smem_u32(&s_full[s]), bytes);
+          bulk_g2s(smem_u32(stage + GK * p.a_bytes), (const uint8_t*)p.packed + (size_t)k0 * p.b_bytes, bytes,
+                   smem_u32(&s_full[s]));
         }
-      }
-      cp_async_arrive_noinc(smem_u32(&s_full[s]));
-      if (++k == p.kv) k = 0;
-      if (++s == S) { s = 0; ++use; }
-      return false;
-    };
-    // The ring is indexed with compile-time constants only: moving a register that is the destination of
-    // a load still in flight would stall on that load and serialise the whole pipeline.
-    bool stop = false;
-    for (int it0 = 0; it0 < total_iters && !stop; it0 += kPrefetch) {
-#pragma unroll
-      for (int j = 0; j < kPrefetch; ++j) {
-        if (it0 + j < total_iters && !stop) {
-          const int cur = nb[j];
-          nb[j] = pf_load();
-          stop = fill_stage(cur);
+        for (int g = 0; g < nk; ++g) {
+          int in_row = tbl[(k0 + g) * 32];
+          if (in_row >= p.n_rows) { bad = true; in_row = -1; }
+          const uint32_t ok = in_row >= 0 ? 16u : 0u;
+          const uint8_t* src = rows + (size_t)(in_row >= 0 ? in_row : 0) * p.row_bytes;
+          const uint32_t dst = smem_u32(stage) + (uint32_t)(g * p.a_bytes) + row_off;
+          for (int c = 0; c < p.kc; ++c) cp_async_16(dst + (uint32_t)c * 2048u, src + c * 16, ok);
         }
+        cp_async_arrive_noinc(smem_u32(&s_full[s]));
+        if (++s == S) { s = 0; ++use; }
       }
+      if (has_next) park_table();
     }
     cp_async_wait_all();
     if (bad && p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
@@ -245,36 +232,37 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       const uint32_t lbo_a = 2048u, sbo_a = 128u;
       const uint32_t lbo_b = (uint32_t)(p.N / 8) * 128u, sbo_b = 128u;
       const int n_mma = p.kc / 2;  // 32 bytes of K per instruction (16 x 16-bit or 32 x 8-bit)
-      if (p.w_resident) mbar_wait(smem_u32(&s_w_full), 0u, abort_flag);
-      int k = 0, blk_i = 0;
+      bool dead = false;
+      if (p.w_resident) dead = !mbar_wait(smem_u32(&s_w_full), 0u, abort_flag);
       int s = 0;
       uint32_t use = 0;
-      for (int it = 0; it < total_iters; ++it) {
-        const int buf = blk_i & 1;
-        if (k == 0) {
-          mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)blk_i >> 1) & 1u) ^ 1u, abort_flag);
-        }
-        mbar_wait(smem_u32(&s_full[s]), use & 1u, abort_flag);
-        if (*abort_flag) break;
-        fence_proxy_async();
-        tc_fence_after();
-        const uint32_t a_addr = smem_u32(stage0 + (size_t)s * stage_bytes);
-        const uint32_t b_addr = p.w_resident ? smem_u32(w_smem + (size_t)k * p.b_bytes) : a_addr + (uint32_t)p.a_bytes;
+      for (int bi = 0; bi < my_blocks && !dead; ++bi) {
+        const int buf = bi & 1;
+        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)bi >> 1) & 1u) ^ 1u, abort_flag)) break;
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.N);
-        for (int j = 0; j < n_mma; ++j) {
-          const uint64_t a_desc = make_smem_desc(a_addr + (uint32_t)j * 2u * lbo_a, lbo_a, sbo_a);
-          const uint64_t b_desc = make_smem_desc(b_addr + (uint32_t)j * 2u * lbo_b, lbo_b, sbo_b);
-          const uint32_t accumulate = (k != 0 || j != 0) ? 1u : 0u;
-          if (p.is_i8) umma_i8(d_tmem, a_desc, b_desc, idesc, accumulate);
-          else umma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
+        for (int grp = 0; grp < groups; ++grp) {
+          if (!mbar_wait(smem_u32(&s_full[s]), use & 1u, abort_flag)) { dead = true; break; }
+          fence_proxy_async();
+          tc_fence_after();
+          const int k0 = grp * GK;
+          const int nk = min(GK, p.kv - k0);
+          const uint32_t stage = smem_u32(stage0 + (size_t)s * stage_bytes);
+          for (int g = 0; g < nk; ++g) {
+            const uint32_t a_addr = stage + (uint32_t)(g * p.a_bytes);
+            const uint32_t b_addr = p.w_resident ? smem_u32(w_smem + (size_t)(k0 + g) * p.b_bytes)
+                                                 : stage + (uint32_t)(GK * p.a_bytes + g * p.b_bytes);
+            for (int j = 0; j < n_mma; ++j) {
+              const uint64_t a_desc = make_smem_desc(a_addr + (uint32_t)j * 2u * lbo_a, lbo_a, sbo_a);
+              const uint64_t b_desc = make_smem_desc(b_addr + (uint32_t)j * 2u * lbo_b, lbo_b, sbo_b);
+              const uint32_t accumulate = (k0 + g != 0 || j != 0) ? 1u : 0u;
+              if (p.is_i8) umma_i8(d_tmem, a_desc, b_desc, idesc, accumulate);
+              else umma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
+            }
+          }
+          umma_commit(smem_u32(&s_empty[s]));   // the slot is free once these MMAs have read it
+          if (++s == S) { s = 0; ++use; }
         }
-        umma_commit(smem_u32(&s_empty[s]));
-        if (++s == S) { s = 0; ++use; }
-        if (++k == p.kv) {
-          umma_commit(smem_u32(&s_acc_full[buf]));
-          k = 0;
-          ++blk_i;
-        }
+        if (!dead) umma_commit(smem_u32(&s_acc_full[buf]));
       }
     }
     __syncwarp();
@@ -284,8 +272,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     for (int blk_i = 0; blk_i < my_blocks; ++blk_i) {
       const int buf = blk_i & 1;
       const int64_t blk = (int64_t)blockIdx.x + (int64_t)blk_i * gridDim.x;
-      mbar_wait(smem_u32(&s_acc_full[buf]), ((uint32_t)blk_i >> 1) & 1u, abort_flag);
-      if (__any_sync(0xffffffffu, *abort_flag != 0)) break;  // warp-uniform: tcgen05.ld is warp-wide
+      const bool ok = mbar_wait(smem_u32(&s_acc_full[buf]), ((uint32_t)blk_i >> 1) & 1u, abort_flag);
+      if (__any_sync(0xffffffffu, !ok)) break;  // warp-uniform: tcgen05.ld is warp-wide
       tc_fence_after();
       const int64_t r = blk * kBlockRows + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * p.N);
@@ -316,8 +304,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   if (s_abort) {
     // let copies still in flight land before the CTA's shared memory is released
     if (warp < 4) cp_async_wait_all();
-    const uint64_t t0 = global_timer_ns();
-    while (global_timer_ns() - t0 < 2000000ull) { }
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000ll) { }
     if (tid == 0 && p.status) atomicOr(p.status, SPH_STATUS_TIMEOUT);
     __syncthreads();
   }
@@ -378,10 +366,15 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
   while (cols < 2 * N) cols <<= 1;
   p.tmem_cols = cols;
   p.num_blocks = (int)div_up64(n_out, kBlockRows);
-  // weights resident when they leave room for at least 4 A stages
+  // offsets per stage: aim at ~16 KB of gathered rows per stage so barrier traffic is amortised
+  int gk = 16384 / p.a_bytes;
+  if (gk < 1) gk = 1;
+  if (gk > 4) gk = 4;
+  p.gk = gk;
+  // weights resident when they leave room for at least 4 stages of gathered rows
   const int w_all = kv * p.b_bytes;
-  p.w_resident = (w_all + 4 * p.a_bytes <= kSmemBudget) ? 1 : 0;
-  const int stage_bytes = p.a_bytes + (p.w_resident ? 0 : p.b_bytes);
+  p.w_resident = (w_all + 4 * gk * p.a_bytes <= kSmemBudget) ? 1 : 0;
+  const int stage_bytes = gk * (p.a_bytes + (p.w_resident ? 0 : p.b_bytes));
   int avail = kSmemBudget - (p.w_resident ? w_all : 0);
   int stages = avail / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;

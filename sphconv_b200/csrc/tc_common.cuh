@@ -46,17 +46,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;  // 200 ms: far beyond any healthy wait
+constexpr long long kWaitLimitCycles = 400ll * 1000ll * 1000ll;  // ~0.2 s of SM clocks: far beyond any healthy wait
 
 // Bounded wait.  `abort_flag` is a CTA-shared int: once any thread has timed out every later wait
-// returns at once.  Returns true when the phase completed.
+// returns at once.  Returns true when the phase completed.  The common case never reads a clock:
+// the bound is only armed after a burst of failed polls (reading %globaltimer costs about a microsecond,
+// which would serialise a pipeline that waits once per stage).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  while (true) {
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+  }
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
     if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
+    if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;
       return false;
     }
