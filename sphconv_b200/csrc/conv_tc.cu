@@ -2,21 +2,29 @@
 //
 //   out[r,:] = epilogue( sum_k rows[nbr[k][r], :] @ W[k] )          r in [0, n_out)
 //
-// A CTA owns 128 consecutive output rows at a time (UMMA M = 128) and is persistent over row blocks.
-// For every kernel offset k it builds the A operand [128 x K_ch] by gathering the neighbour rows with
-// 16-byte cp.async copies straight into the UMMA core-matrix layout (absent neighbours are zero-filled
-// without touching memory), multiplies by W[k] ([N_ch x K_ch], K-major, pre-packed) and accumulates in
-// TMEM; after the last offset four epilogue warps read the accumulator back, apply scale/bias/ReLU and
-// store whole rows.  There is no scatter, no atomic and the output is written exactly once
+// A tcgen05.mma costs about 200 SM cycles to issue whatever its shape (measured on B200 for every
+// M in {64,128}, N in 16..256), so the instruction has to be as large as the problem allows.  The
+// channel counts here are small (<= 128) and the row count is huge, so the product is computed
+// transposed:  D^T[oC x 256 rows] += W[k]^T[oC x iC] * X_k^T[iC x 256 rows]
+//   A operand = W[k]^T, M = oC padded to 64 or 128, K-major, pre-packed once per weight;
+//   B operand = the 256 gathered neighbour rows of offset k, N = 256, K-major: each row is copied with
+//               16-byte cp.async straight into the UMMA core-matrix layout (absent neighbours are
+//               zero-filled without touching memory);
+//   D         = fp32 / int32 accumulator in TMEM, lane = output channel, column = output row.
+// A CTA owns 256 consecutive output rows at a time and is persistent over such tiles.  After the last
+// offset four epilogue warps read the accumulator back, apply scale/bias/ReLU, transpose through shared
+// memory and store whole rows.  No scatter, no atomics, every output row is written exactly once
 // (the reference does a read-modify-write of the output per 8 pairs, include/sphconv/iterator.cu.h:1467-1625,
 // driven by the per-tile loop of include/sphconv/rule_conv_kernel.cu.h:91-153).
 //
-// Warp roles (288 threads): warps 0-3 gather, warp 4 issues the MMAs (one thread) and owns TMEM,
-// warps 5-8 run the epilogue.  Stages are handed over with mbarriers; the accumulator is double
-// buffered in TMEM so the epilogue of block i overlaps the MMAs of block i+1.
+// Warp roles (288 threads): warps 0-3 gather (thread t owns tile rows t and t+128), warp 4 issues the
+// MMAs (one thread) and owns TMEM, warps 5-8 run the epilogue.  Stages are handed over with mbarriers;
+// the accumulator is double buffered in TMEM (2 x 256 columns) so the epilogue of tile i overlaps the
+// MMAs of tile i+1.
 //
 // Shared-memory operand layout (no swizzle): 8-row x 16-byte core matrices of 128 contiguous bytes;
-// A: core (row group g, chunk c) at c*2048 + g*128; B: core (channel group gn, chunk c) at c*(N/8)*128 + gn*128.
+// rows: core (row group g, chunk c) at c*4096 + g*128; weights: core (channel group gn, chunk c) at
+// c*(MP/8)*128 + gn*128.
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -28,85 +36,51 @@ namespace {
 
 using namespace tc;
 
-constexpr int kTcMaxKV = 32;       // kernel volume the tensor-core kernel handles (3x3x3 = 27)
+constexpr int kTcMaxKV = 32;        // kernel volume the tensor-core kernel handles (3x3x3 = 27)
 constexpr int kTcThreads = 288;
 constexpr int kProducerThreads = 128;
-constexpr int kBlockRows = 128;
+constexpr int kTileRows = 256;      // output rows per tile = UMMA N
+constexpr int kSubRows = 64;        // rows transposed through shared memory at a time in the epilogue
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 227 * 1024 - 2048 - 4 * kTcMaxKV * 32 * 4;   // minus barriers and the table buffer
+constexpr int kSmemTotal = 227 * 1024 - 2048;   // dynamic shared memory available next to the static part
+constexpr uint32_t kRowsLbo = kTileRows * 16;   // byte distance between K-adjacent core matrices of the row tile
 
 struct TcParams {
   const void* rows;
-  const void* packed;   // [KV][N_ch x K_ch] UMMA images
+  const void* packed;   // [KV] images of W[k]^T, each MP x K_ch, K-major
   const int* nbr;       // [KV][n_out]
   int64_t n_rows, n_out;
   int kv, K, N;         // channels gathered / produced
+  int MP;               // N padded to the UMMA M (64 or 128)
   int row_bytes;        // K * elem bytes
   int kc;               // 16-byte chunks per gathered row
   int stages;
+  int gk;               // kernel offsets gathered per pipeline stage
   int w_resident;       // all KV weight images live in shared memory
-  int a_bytes, b_bytes; // per-offset operand bytes
+  int x_bytes, w_bytes; // per-offset operand bytes: gathered rows, weight image
   int flip_k;
   int is_i8, is_bf16;
   const float* scale;
   const float* bias;
   int relu;
   void* out;
-  int out_dtype;
+  int out_dtype, out_esize;
   int* status;
-  int tmem_cols;
-  int num_blocks;
-  int gk;               // kernel offsets gathered per pipeline stage
+  int num_tiles;
+  int tbl_off, stg_off, w_off, stage_off;   // dynamic shared memory layout (byte offsets)
+  long long* dbg_out;   // optional per-CTA wait-cycle counters (development aid; null in normal use)
 };
 
-__device__ __forceinline__ void store16(void* out, int out_dtype, int64_t elem_idx, const float (&v)[16]) {
+__device__ __forceinline__ void stage_store(uint8_t* dst, int out_dtype, float v) {
   switch (out_dtype) {
-    case SPH_F32: {
-      float4* p = (float4*)((float*)out + elem_idx);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) p[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-      break;
-    }
-    case SPH_F16: {
-      uint4* p = (uint4*)((__half*)out + elem_idx);
-      uint32_t w[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-        w[j] = *(uint32_t*)&h;
-      }
-      p[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      p[1] = make_uint4(w[4], w[5], w[6], w[7]);
-      break;
-    }
-    case SPH_BF16: {
-      uint4* p = (uint4*)((__nv_bfloat16*)out + elem_idx);
-      uint32_t w[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-        w[j] = *(uint32_t*)&h;
-      }
-      p[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      p[1] = make_uint4(w[4], w[5], w[6], w[7]);
-      break;
-    }
-    default: {
-      uint32_t w[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t acc = 0;
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          float r = fminf(fmaxf(rintf(v[4 * j + b]), -127.f), 127.f);
-          acc |= ((uint32_t)(int)r & 0xffu) << (8 * b);
-        }
-        w[j] = acc;
-      }
-      *(uint4*)((int8_t*)out + elem_idx) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
+    case SPH_F32: *(float*)dst = v; break;
+    case SPH_F16: *(__half*)dst = __float2half_rn(v); break;
+    case SPH_BF16: *(__nv_bfloat16*)dst = __float2bfloat16_rn(v); break;
+    default: *(int8_t*)dst = (int8_t)(int)fminf(fmaxf(rintf(v), -127.f), 127.f);
   }
 }
+
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -117,17 +91,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   __shared__ __align__(8) uint64_t s_w_full;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ int s_tbl[4][kTcMaxKV][32];   // per producer warp: neighbour-table entries of the current row block
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int S = p.stages;
-  const int GK = p.gk;                                             // kernel offsets per pipeline stage
-  const int stage_bytes = GK * (p.a_bytes + (p.w_resident ? 0 : p.b_bytes));
-  uint8_t* w_smem = smem;                                          // resident weights (if any)
-  uint8_t* stage0 = smem + (p.w_resident ? p.kv * p.b_bytes : 0);  // multiple of 128 bytes either way
-  const int groups = (p.kv + GK - 1) / GK;                         // stages per row block
+  const int GK = p.gk;
+  const int stage_bytes = GK * (p.x_bytes + (p.w_resident ? 0 : p.w_bytes));
+  int* s_tbl = (int*)(smem + p.tbl_off);          // [kv][256] neighbour rows of the current tile
+  uint8_t* s_stg = smem + p.stg_off;              // [64][N] epilogue transpose buffer
+  uint8_t* w_smem = smem + p.w_off;               // resident weight images (if any)
+  uint8_t* stage0 = smem + p.stage_off;
+  const int groups = (p.kv + GK - 1) / GK;        // stages per tile
 
   if (tid == 0) {
     s_abort = 0;
@@ -143,7 +118,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     mbar_init_fence();
   }
   if (warp == 4) {
-    tmem_alloc(smem_u32(&s_tmem_base), (uint32_t)p.tmem_cols);
+    tmem_alloc(smem_u32(&s_tmem_base), 512u);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -152,41 +127,45 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
 
-  // blocks handled by this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
-  const int my_blocks = (p.num_blocks - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  // tiles handled by this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
+  const int my_tiles = (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
   if (warp < 4) {
     // ======================= gather producers =======================
-    // Lane <-> output row (32*warp + lane of the block).  The per-stage instruction stream of a producer
-    // warp is the pipeline's critical path, so it is kept to: one barrier poll, one shared-memory read
-    // of the neighbour row id, kc 16-byte cp.async per offset, one arrive.  The neighbour-table entries
-    // of the NEXT block are loaded into registers while the current block is gathered and parked in
-    // shared memory at the block boundary, so no global-load latency sits on that path.
+    // The per-stage instruction stream of a producer warp sits on the pipeline's critical path, so it
+    // is kept to: one barrier poll, a shared-memory read of the neighbour row id, kc cp.async per row,
+    // one arrive.  The neighbour-table entries of the NEXT tile are loaded into registers while the
+    // current tile is gathered and parked in shared memory at the tile boundary, so no global-load
+    // latency sits on that path.
     if (p.w_resident && tid == 0) {
-      const uint32_t bytes = (uint32_t)(p.kv * p.b_bytes);
-      mbar_arrive_expect_tx(smem_u32(&s_w_full), bytes);
-      // one bulk copy per offset keeps each transfer well under the mbarrier tx-count limit
-      for (int k = 0; k < p.kv; ++k)
-        bulk_g2s(smem_u32(w_smem + (size_t)k * p.b_bytes), (const uint8_t*)p.packed + (size_t)k * p.b_bytes,
-                 (uint32_t)p.b_bytes, smem_u32(&s_w_full));
+      mbar_arrive_expect_tx(smem_u32(&s_w_full), (uint32_t)(p.kv * p.w_bytes));
+      for (int k = 0; k < p.kv; ++k)   // one bulk copy per offset keeps each transfer small
+        bulk_g2s(smem_u32(w_smem + (size_t)k * p.w_bytes), (const uint8_t*)p.packed + (size_t)k * p.w_bytes,
+                 (uint32_t)p.w_bytes, smem_u32(&s_w_full));
     }
     const uint8_t* rows = (const uint8_t*)p.rows;
-    int* tbl = &s_tbl[warp][0][lane];   // entry of offset k at tbl[k * 32]
-    int tmp[kTcMaxKV];
-    auto load_table = [&](int blk) {
-      const int64_t r = (int64_t)blk * kBlockRows + warp * 32 + lane;
+    int* tbl = s_tbl + tid;   // entry of (offset k, tile row tid + 128*h) at tbl[k*256 + 128*h]
+    int tmp0[kTcMaxKV], tmp1[kTcMaxKV];
+    auto load_table = [&](int tile) {
+      const int64_t r0 = (int64_t)tile * kTileRows + tid;
+      const int64_t r1 = r0 + 128;
 #pragma unroll
       for (int k = 0; k < kTcMaxKV; ++k) {
         if (k < p.kv) {
-          const int tk = p.flip_k ? p.kv - 1 - k : k;
-          tmp[k] = r < p.n_out ? __ldg(p.nbr + (int64_t)tk * p.n_out + r) : -1;
+          const int64_t base = (int64_t)(p.flip_k ? p.kv - 1 - k : k) * p.n_out;
+          tmp0[k] = r0 < p.n_out ? __ldg(p.nbr + base + r0) : -1;
+          tmp1[k] = r1 < p.n_out ? __ldg(p.nbr + base + r1) : -1;
         }
       }
     };
     auto park_table = [&]() {
 #pragma unroll
-      for (int k = 0; k < kTcMaxKV; ++k)
-        if (k < p.kv) tbl[k * 32] = tmp[k];
+      for (int k = 0; k < kTcMaxKV; ++k) {
+        if (k < p.kv) {
+          tbl[k * kTileRows] = tmp0[k];
+          tbl[k * kTileRows + 128] = tmp1[k];
+        }
+      }
     };
     load_table((int)blockIdx.x);
     park_table();
@@ -194,108 +173,155 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     int s = 0;
     uint32_t use = 0;
     bool bad = false, dead = false;
-    const uint32_t row_off = (uint32_t)((warp * 32 + lane) * 16);
-    for (int bi = 0; bi < my_blocks && !dead; ++bi) {
-      const bool has_next = bi + 1 < my_blocks;
-      if (has_next) load_table((int)blockIdx.x + (bi + 1) * (int)gridDim.x);
+    long long t_wait_empty = 0;
+    const long long t_begin = p.dbg_out ? clock64() : 0;
+    const uint32_t row_off = (uint32_t)tid * 16u;   // rows t and t+128: core-matrix offsets t*16 and t*16 + 2048
+    for (int ti = 0; ti < my_tiles && !dead; ++ti) {
+      const bool has_next = ti + 1 < my_tiles;
+      if (has_next) load_table((int)blockIdx.x + (ti + 1) * (int)gridDim.x);
       for (int grp = 0; grp < groups; ++grp) {
+        const long long tw0 = p.dbg_out ? clock64() : 0;
         if (!mbar_wait(smem_u32(&s_empty[s]), (use & 1u) ^ 1u, abort_flag)) { dead = true; break; }
+        if (p.dbg_out) t_wait_empty += clock64() - tw0;
         uint8_t* stage = stage0 + (size_t)s * stage_bytes;
         const int k0 = grp * GK;
         const int nk = min(GK, p.kv - k0);
         if (!p.w_resident && tid == 0) {
-          const uint32_t bytes = (uint32_t)(nk * p.b_bytes);
+          const uint32_t bytes = (uint32_t)(nk * p.w_bytes);
           mbar_arrive_expect_tx(smem_u32(&s_full[s]), bytes);
-          bulk_g2s(smem_u32(stage + GK * p.a_bytes), (const uint8_t*)p.packed + (size_t)k0 * p.b_bytes, bytes,
+          bulk_g2s(smem_u32(stage + GK * p.x_bytes), (const uint8_t*)p.packed + (size_t)k0 * p.w_bytes, bytes,
                    smem_u32(&s_full[s]));
         }
         for (int g = 0; g < nk; ++g) {
-          int in_row = tbl[(k0 + g) * 32];
-          if (in_row >= p.n_rows) { bad = true; in_row = -1; }
-          const uint32_t ok = in_row >= 0 ? 16u : 0u;
-          const uint8_t* src = rows + (size_t)(in_row >= 0 ? in_row : 0) * p.row_bytes;
-          const uint32_t dst = smem_u32(stage) + (uint32_t)(g * p.a_bytes) + row_off;
-          for (int c = 0; c < p.kc; ++c) cp_async_16(dst + (uint32_t)c * 2048u, src + c * 16, ok);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            int in_row = tbl[(k0 + g) * kTileRows + 128 * h];
+            if (in_row >= p.n_rows) { bad = true; in_row = -1; }
+            const uint32_t ok = in_row >= 0 ? 16u : 0u;
+            const uint8_t* src = rows + (size_t)(in_row >= 0 ? in_row : 0) * p.row_bytes;
+            const uint32_t dst = smem_u32(stage) + (uint32_t)(g * p.x_bytes) + row_off + 2048u * h;
+            for (int c = 0; c < p.kc; ++c) cp_async_16(dst + (uint32_t)c * kRowsLbo, src + c * 16, ok);
+          }
         }
         cp_async_arrive_noinc(smem_u32(&s_full[s]));
         if (++s == S) { s = 0; ++use; }
       }
-      if (has_next) park_table();
+      if (has_next && !dead) park_table();
+    }
+    if (p.dbg_out && tid == 0) {
+      p.dbg_out[blockIdx.x * 8 + 0] = t_wait_empty;
+      p.dbg_out[blockIdx.x * 8 + 4] = clock64() - t_begin;
     }
     cp_async_wait_all();
     if (bad && p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
   } else if (warp == 4) {
     // ======================= MMA issuer =======================
     if (lane == 0) {
-      const uint32_t idesc = p.is_i8 ? make_idesc(2u, 1u, 0u, 0u, kBlockRows, (uint32_t)p.N)
-                                     : make_idesc(1u, p.is_bf16 ? 1u : 0u, 0u, 0u, kBlockRows, (uint32_t)p.N);
-      const uint32_t lbo_a = 2048u, sbo_a = 128u;
-      const uint32_t lbo_b = (uint32_t)(p.N / 8) * 128u, sbo_b = 128u;
+      const uint32_t idesc = p.is_i8 ? make_idesc(2u, 1u, 0u, 0u, (uint32_t)p.MP, kTileRows)
+                                     : make_idesc(1u, p.is_bf16 ? 1u : 0u, 0u, 0u, (uint32_t)p.MP, kTileRows);
+      const uint32_t lbo_w = (uint32_t)(p.MP / 8) * 128u;
       const int n_mma = p.kc / 2;  // 32 bytes of K per instruction (16 x 16-bit or 32 x 8-bit)
       bool dead = false;
       if (p.w_resident) dead = !mbar_wait(smem_u32(&s_w_full), 0u, abort_flag);
       int s = 0;
       uint32_t use = 0;
-      for (int bi = 0; bi < my_blocks && !dead; ++bi) {
-        const int buf = bi & 1;
-        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)bi >> 1) & 1u) ^ 1u, abort_flag)) break;
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.N);
+      long long t_full = 0, t_acc = 0, t_issue = 0;
+      for (int ti = 0; ti < my_tiles && !dead; ++ti) {
+        const int buf = ti & 1;
+        const long long ta0 = p.dbg_out ? clock64() : 0;
+        if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)ti >> 1) & 1u) ^ 1u, abort_flag)) break;
+        if (p.dbg_out) t_acc += clock64() - ta0;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTileRows);
         for (int grp = 0; grp < groups; ++grp) {
+          const long long tf0 = p.dbg_out ? clock64() : 0;
           if (!mbar_wait(smem_u32(&s_full[s]), use & 1u, abort_flag)) { dead = true; break; }
-          fence_proxy_async();
+          const long long tf1 = p.dbg_out ? clock64() : 0;
           tc_fence_after();
           const int k0 = grp * GK;
           const int nk = min(GK, p.kv - k0);
           const uint32_t stage = smem_u32(stage0 + (size_t)s * stage_bytes);
           for (int g = 0; g < nk; ++g) {
-            const uint32_t a_addr = stage + (uint32_t)(g * p.a_bytes);
-            const uint32_t b_addr = p.w_resident ? smem_u32(w_smem + (size_t)(k0 + g) * p.b_bytes)
-                                                 : stage + (uint32_t)(GK * p.a_bytes + g * p.b_bytes);
+            const uint32_t x_addr = stage + (uint32_t)(g * p.x_bytes);
+            const uint32_t w_addr = p.w_resident ? smem_u32(w_smem + (size_t)(k0 + g) * p.w_bytes)
+                                                 : stage + (uint32_t)(GK * p.x_bytes + g * p.w_bytes);
             for (int j = 0; j < n_mma; ++j) {
-              const uint64_t a_desc = make_smem_desc(a_addr + (uint32_t)j * 2u * lbo_a, lbo_a, sbo_a);
-              const uint64_t b_desc = make_smem_desc(b_addr + (uint32_t)j * 2u * lbo_b, lbo_b, sbo_b);
+              const uint64_t a_desc = make_smem_desc(w_addr + (uint32_t)j * 2u * lbo_w, lbo_w, 128u);
+              const uint64_t b_desc = make_smem_desc(x_addr + (uint32_t)j * 2u * kRowsLbo, kRowsLbo, 128u);
               const uint32_t accumulate = (k0 + g != 0 || j != 0) ? 1u : 0u;
               if (p.is_i8) umma_i8(d_tmem, a_desc, b_desc, idesc, accumulate);
               else umma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
             }
           }
           umma_commit(smem_u32(&s_empty[s]));   // the slot is free once these MMAs have read it
+          if (p.dbg_out) {
+            t_full += tf1 - tf0;
+            t_issue += clock64() - tf1;
+          }
           if (++s == S) { s = 0; ++use; }
         }
         if (!dead) umma_commit(smem_u32(&s_acc_full[buf]));
+      }
+      if (p.dbg_out) {
+        p.dbg_out[blockIdx.x * 8 + 1] = t_full;
+        p.dbg_out[blockIdx.x * 8 + 2] = t_acc;
+        p.dbg_out[blockIdx.x * 8 + 6] = t_issue;
       }
     }
     __syncwarp();
   } else {
     // ======================= epilogue =======================
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    for (int blk_i = 0; blk_i < my_blocks; ++blk_i) {
-      const int buf = blk_i & 1;
-      const int64_t blk = (int64_t)blockIdx.x + (int64_t)blk_i * gridDim.x;
-      const bool ok = mbar_wait(smem_u32(&s_acc_full[buf]), ((uint32_t)blk_i >> 1) & 1u, abort_flag);
-      if (__any_sync(0xffffffffu, !ok)) break;  // warp-uniform: tcgen05.ld is warp-wide
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int et = q * 32 + lane;                 // 0..127 among the epilogue threads
+    // accumulator row (= output channel) held by this thread's TMEM lane
+    const int oc = p.MP == 64 ? (lane < 16 ? 16 * q + lane : -1) : 32 * q + lane;
+    const bool has_oc = oc >= 0 && oc < p.N;
+    const float sc = (has_oc && p.scale) ? __ldg(p.scale + oc) : 1.f;
+    const float bi = (has_oc && p.bias) ? __ldg(p.bias + oc) : 0.f;
+    const int row_pitch = p.N * p.out_esize;      // bytes of one output row; the staging buffer uses the same pitch
+    long long t_epi_wait = 0;
+    for (int ti = 0; ti < my_tiles; ++ti) {
+      const int buf = ti & 1;
+      const int64_t tile = (int64_t)blockIdx.x + (int64_t)ti * gridDim.x;
+      const long long te0 = p.dbg_out ? clock64() : 0;
+      const bool ok = mbar_wait(smem_u32(&s_acc_full[buf]), ((uint32_t)ti >> 1) & 1u, abort_flag);
+      if (p.dbg_out) t_epi_wait += clock64() - te0;
+      if (__any_sync(0xffffffffu, !ok)) break;    // warp-uniform: tcgen05.ld is warp-wide
       tc_fence_after();
-      const int64_t r = blk * kBlockRows + q * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * p.N);
-      for (int c0 = 0; c0 < p.N; c0 += 16) {
-        uint32_t raw[16];
-        tmem_ld16(taddr + (uint32_t)c0, raw);
-        tmem_ld_wait();
-        float v[16];
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTileRows);
+      for (int sub = 0; sub < kTileRows / kSubRows; ++sub) {
+        const int64_t row0 = tile * kTileRows + sub * kSubRows;
+        if (row0 >= p.n_out) break;               // uniform over the four warps
+        for (int c0 = 0; c0 < kSubRows; c0 += 16) {
+          uint32_t raw[16];
+          tmem_ld16(taddr + (uint32_t)(sub * kSubRows + c0), raw);
+          tmem_ld_wait();
+          if (has_oc) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float x = p.is_i8 ? (float)(int)raw[j] : __uint_as_float(raw[j]);
-          if (p.scale) x *= __ldg(p.scale + c0 + j);
-          if (p.bias) x += __ldg(p.bias + c0 + j);
-          if (p.relu) x = fmaxf(x, 0.f);
-          v[j] = x;
+            for (int j = 0; j < 16; ++j) {
+              float x = p.is_i8 ? (float)(int)raw[j] : __uint_as_float(raw[j]);
+              x = x * sc + bi;
+              if (p.relu) x = fmaxf(x, 0.f);
+              stage_store(s_stg + (c0 + j) * row_pitch + oc * p.out_esize, p.out_dtype, x);
+            }
+          }
         }
-        if (r < p.n_out) store16(p.out, p.out_dtype, r * p.N + c0, v);
+        epilogue_bar();
+        // the 64 rows are one contiguous range of the output: copy it out with 16-byte stores
+        const int64_t rows_here = min((int64_t)kSubRows, p.n_out - row0);
+        const int nbytes = (int)rows_here * row_pitch;
+        uint8_t* gdst = (uint8_t*)p.out + row0 * row_pitch;
+        const int nvec = nbytes & ~15;
+        for (int off = et * 16; off < nvec; off += 128 * 16)
+          *(uint4*)(gdst + off) = *(const uint4*)(s_stg + off);
+        for (int off = nvec + et; off < nbytes; off += 128) gdst[off] = s_stg[off];   // ragged last rows
+        epilogue_bar();
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_acc_empty[buf]));
     }
+    if (p.dbg_out && warp == 5 && lane == 0) p.dbg_out[blockIdx.x * 8 + 3] = t_epi_wait;
   }
 
   // ---- wind down: every thread arrives here, also after an abort
@@ -311,13 +337,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   }
   if (warp == 4) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    tmem_dealloc(tmem_base, 512u);
   }
 }
 
-// [KV][K][N] row-major weights -> per-offset UMMA image of B = W[k]^T ([N x K], K-major, no swizzle).
+// [KV][K][N] row-major weights -> per-offset UMMA image of W[k]^T ([MP x K], K-major, no swizzle);
+// rows N..MP-1 of every image stay zero (the buffer is cleared first).
 template <typename T>
-__global__ void pack_weight_kernel(const T* __restrict__ w, int kv, int K, int N, T* __restrict__ packed) {
+__global__ void pack_weight_kernel(const T* __restrict__ w, int kv, int K, int N, int MP, T* __restrict__ packed) {
   const int64_t total = (int64_t)kv * K * N;
   const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= total) return;
@@ -325,17 +352,19 @@ __global__ void pack_weight_kernel(const T* __restrict__ w, int kv, int K, int N
   const int ic = (int)((e / N) % K);
   const int k = (int)(e / ((int64_t)N * K));
   const int cpe = 16 / (int)sizeof(T);  // elements per 16-byte chunk
-  const int64_t img = (int64_t)k * K * N;
-  const int64_t off_bytes = (int64_t)(ic / cpe) * (N / 8) * 128 + (oc / 8) * 128 + (oc % 8) * 16 + (ic % cpe) * (int)sizeof(T);
+  const int64_t img = (int64_t)k * K * MP;
+  const int64_t off_bytes = (int64_t)(ic / cpe) * (MP / 8) * 128 + (oc / 8) * 128 + (oc % 8) * 16 + (ic % cpe) * (int)sizeof(T);
   packed[img + off_bytes / (int64_t)sizeof(T)] = w[e];
 }
+
+int padded_m(int N) { return N <= 64 ? 64 : 128; }
 
 bool tc_shape_ok(int dtype, int kv, int K, int N) {
   if (dtype != SPH_F16 && dtype != SPH_BF16 && dtype != SPH_I8) return false;
   const int e = dtype_bytes(dtype);
   const int row_bytes = K * e;
-  if (row_bytes % 32 != 0 || row_bytes < 32 || row_bytes > 512) return false;
-  if (N % 16 != 0 || N < 16 || N > 256) return false;
+  if (row_bytes % 32 != 0 || row_bytes < 32 || row_bytes > 256) return false;
+  if (N % 8 != 0 || N < 8 || N > 128) return false;
   if (kv < 1 || kv > kTcMaxKV) return false;
   return true;
 }
@@ -353,37 +382,47 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
   p.rows = rows; p.packed = packed; p.nbr = nbr;
   p.n_rows = n_rows; p.n_out = n_out;
   p.kv = kv; p.K = K; p.N = N;
+  p.MP = padded_m(N);
   p.row_bytes = K * dtype_bytes(dtype);
   p.kc = p.row_bytes / 16;
-  p.a_bytes = kBlockRows * p.row_bytes;
-  p.b_bytes = N * p.row_bytes;
+  p.x_bytes = kTileRows * p.row_bytes;
+  p.w_bytes = p.MP * p.row_bytes;
   p.flip_k = flip_k;
   p.is_i8 = dtype == SPH_I8;
   p.is_bf16 = dtype == SPH_BF16;
   p.scale = scale; p.bias = bias; p.relu = relu;
-  p.out = out; p.out_dtype = out_dtype; p.status = status;
-  int cols = 32;
-  while (cols < 2 * N) cols <<= 1;
-  p.tmem_cols = cols;
-  p.num_blocks = (int)div_up64(n_out, kBlockRows);
-  // offsets per stage: aim at ~16 KB of gathered rows per stage so barrier traffic is amortised
-  int gk = 16384 / p.a_bytes;
+  p.out = out; p.out_dtype = out_dtype; p.out_esize = dtype_bytes(out_dtype); p.status = status;
+  p.num_tiles = (int)div_up64(n_out, kTileRows);
+  // dynamic shared memory: neighbour table, epilogue transpose buffer, (resident weights), stages
+  int off = 0;
+  p.tbl_off = off; off += kv * kTileRows * (int)sizeof(int);
+  p.stg_off = off; off += kSubRows * N * p.out_esize;
+  off = (off + 1023) & ~1023;
+  p.w_off = off;
+  // offsets per stage: aim at 16 KB or more of gathered rows per stage so barrier traffic is amortised
+  int gk = 16384 / p.x_bytes;
   if (gk < 1) gk = 1;
   if (gk > 4) gk = 4;
   p.gk = gk;
-  // weights resident when they leave room for at least 4 stages of gathered rows
-  const int w_all = kv * p.b_bytes;
-  p.w_resident = (w_all + 4 * gk * p.a_bytes <= kSmemBudget) ? 1 : 0;
-  const int stage_bytes = gk * (p.a_bytes + (p.w_resident ? 0 : p.b_bytes));
-  int avail = kSmemBudget - (p.w_resident ? w_all : 0);
-  int stages = avail / stage_bytes;
+  const int w_all = kv * p.w_bytes;
+  p.w_resident = (off + w_all + 4 * gk * p.x_bytes <= kSmemTotal) ? 1 : 0;
+  if (p.w_resident) off += w_all;
+  p.stage_off = off;
+  const int stage_bytes = gk * (p.x_bytes + (p.w_resident ? 0 : p.w_bytes));
+  int stages = (kSmemTotal - off) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) {
     set_error("conv_gather_tc: operands do not fit in shared memory");
     return SPH_ERR_UNSUPPORTED;
   }
+  {
+    const char* st_env = getenv("SPH_TC_STAGES");
+    if (st_env && atoi(st_env) >= 2 && atoi(st_env) <= stages) stages = atoi(st_env);
+    const char* dp = getenv("SPH_TC_DBGPTR");
+    p.dbg_out = dp ? (long long*)strtoull(dp, nullptr, 16) : nullptr;
+  }
   p.stages = stages;
-  const int smem_bytes = (p.w_resident ? w_all : 0) + stages * stage_bytes;
+  const int smem_bytes = off + stages * stage_bytes;
 
   static int s_sms = 0;
   if (s_sms == 0) {
@@ -392,13 +431,8 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
     SPH_CUDA(cudaDeviceGetAttribute(&s_sms, cudaDevAttrMultiProcessorCount, dev));
   }
   SPH_CUDA(cudaFuncSetAttribute(conv_gather_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-  int occ = 1;
-  SPH_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, conv_gather_tc_kernel, kTcThreads, smem_bytes));
-  if (occ < 1) occ = 1;
-  if (occ > 512 / cols) occ = 512 / cols;  // every resident CTA holds `cols` TMEM columns
-  if (occ > 2) occ = 2;
-  int grid = s_sms * occ;
-  if (grid > p.num_blocks) grid = p.num_blocks;
+  // every CTA takes all 512 TMEM columns, so exactly one is resident per SM
+  int grid = s_sms < p.num_tiles ? s_sms : p.num_tiles;
   if (grid < 1) return SPH_OK;
   conv_gather_tc_kernel<<<grid, kTcThreads, smem_bytes, st>>>(p);
   SPH_LAUNCH_CHECK();
@@ -408,7 +442,7 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
 bool conv_tc_supported(int dtype, int kv, int K, int N) { return tc_shape_ok(dtype, kv, K, N); }
 
 int64_t packed_weight_bytes(int dtype, int kv, int K, int N) {
-  return (int64_t)kv * K * N * dtype_bytes(dtype);
+  return (int64_t)kv * K * padded_m(N) * dtype_bytes(dtype);
 }
 
 int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cudaStream_t st) {
@@ -416,11 +450,15 @@ int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cu
     set_error("pack_weight: unsupported dtype/shape");
     return SPH_ERR_UNSUPPORTED;
   }
+  const int MP = padded_m(N);
+  SPH_CUDA(cudaMemsetAsync(packed, 0, (size_t)packed_weight_bytes(dtype, kv, K, N), st));
   const int64_t total = (int64_t)kv * K * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)div_up64(total, threads);
-  if (dtype == SPH_I8) pack_weight_kernel<int8_t><<<blocks, threads, 0, st>>>((const int8_t*)w, kv, K, N, (int8_t*)packed);
-  else pack_weight_kernel<uint16_t><<<blocks, threads, 0, st>>>((const uint16_t*)w, kv, K, N, (uint16_t*)packed);
+  if (dtype == SPH_I8)
+    pack_weight_kernel<int8_t><<<blocks, threads, 0, st>>>((const int8_t*)w, kv, K, N, MP, (int8_t*)packed);
+  else
+    pack_weight_kernel<uint16_t><<<blocks, threads, 0, st>>>((const uint16_t*)w, kv, K, N, MP, (uint16_t*)packed);
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
