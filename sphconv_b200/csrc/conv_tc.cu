@@ -17,13 +17,13 @@
 // (the reference does a read-modify-write of the output per 8 pairs, include/sphconv/iterator.cu.h:1467-1625,
 // driven by the per-tile loop of include/sphconv/rule_conv_kernel.cu.h:91-153).
 //
-// Warp roles (288 threads): warps 0-3 gather (thread t owns tile rows t and t+128), warp 4 issues the
-// MMAs (one thread) and owns TMEM, warps 5-8 run the epilogue.  Stages are handed over with mbarriers;
+// Warp roles (416 threads): warps 0-7 gather (32 rows of the tile each), warp 8 issues the MMAs (one
+// thread) and owns TMEM, warps 9-12 run the epilogue.  Stages are handed over with mbarriers;
 // the accumulator is double buffered in TMEM (2 x 256 columns) so the epilogue of tile i overlaps the
 // MMAs of tile i+1.
 //
 // Shared-memory operand layout (no swizzle): 8-row x 16-byte core matrices of 128 contiguous bytes;
-// rows: core (row group g, chunk c) at c*4096 + g*128; weights: core (channel group gn, chunk c) at
+// rows: core (row group g, chunk c) at c*4112 + g*128; weights: core (channel group gn, chunk c) at
 // c*(MP/8)*128 + gn*128.
 #include <stdlib.h>
 
@@ -37,13 +37,19 @@ namespace {
 using namespace tc;
 
 constexpr int kTcMaxKV = 32;        // kernel volume the tensor-core kernel handles (3x3x3 = 27)
-constexpr int kTcThreads = 288;
-constexpr int kProducerThreads = 128;
 constexpr int kTileRows = 256;      // output rows per tile = UMMA N
+constexpr int kProducerWarps = 8;    // gather warps; each owns 256 / 8 = 32 rows of the tile
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kMmaWarp = kProducerWarps;
+constexpr int kTcThreads = (kProducerWarps + 1 + 4) * 32;
+constexpr int kRowsPerWarp = kTileRows / kProducerWarps;
 constexpr int kSubRows = 64;        // rows transposed through shared memory at a time in the epilogue
 constexpr int kMaxStages = 8;
 constexpr int kSmemTotal = 227 * 1024 - 2048;   // dynamic shared memory available next to the static part
-constexpr uint32_t kRowsLbo = kTileRows * 16;   // byte distance between K-adjacent core matrices of the row tile
+// Byte distance between K-adjacent core matrices of the gathered-row tile.  The extra 16 bytes skew the
+// chunks of one row across the shared-memory banks, so the 32 lanes of a gather instruction (a few rows x
+// all their chunks) write without bank conflicts.
+constexpr uint32_t kRowsLbo = kTileRows * 16 + 16;
 
 struct TcParams {
   const void* rows;
@@ -68,7 +74,7 @@ struct TcParams {
   int* status;
   int num_tiles;
   int tbl_off, stg_off, w_off, stage_off;   // dynamic shared memory layout (byte offsets)
-  long long* dbg_out;   // optional per-CTA wait-cycle counters (development aid; null in normal use)
+  int debug;            // development switches (environment SPH_TC_DEBUG); 0 in normal use
 };
 
 __device__ __forceinline__ void stage_store(uint8_t* dst, int out_dtype, float v) {
@@ -107,7 +113,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(&s_full[s]), kProducerThreads + (p.w_resident ? 0 : 1));
+      mbar_init(smem_u32(&s_full[s]), kProducerWarps + (p.w_resident ? 0 : 1));   // one arrival per gather warp
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -117,7 +123,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     mbar_init(smem_u32(&s_w_full), 1);
     mbar_init_fence();
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&s_tmem_base), 512u);
     tmem_relinquish();
   }
@@ -130,7 +136,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   // tiles handled by this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
   const int my_tiles = (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
-  if (warp < 4) {
+  if (warp < kProducerWarps) {
     // ======================= gather producers =======================
     // The per-stage instruction stream of a producer warp sits on the pipeline's critical path, so it
     // is kept to: one barrier poll, a shared-memory read of the neighbour row id, kc cp.async per row,
@@ -144,45 +150,54 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
                  (uint32_t)p.w_bytes, smem_u32(&s_w_full));
     }
     const uint8_t* rows = (const uint8_t*)p.rows;
-    int* tbl = s_tbl + tid;   // entry of (offset k, tile row tid + 128*h) at tbl[k*256 + 128*h]
-    int tmp0[kTcMaxKV], tmp1[kTcMaxKV];
+    // warp w owns tile rows [32w, 32w+32); its lane l loads and parks the table entries of row 32w+l
+    int* tbl = s_tbl + warp * kRowsPerWarp + lane;   // entry of (offset k, row 32w + l) at tbl[k*256]
+    int tmp0[kTcMaxKV];
     auto load_table = [&](int tile) {
-      const int64_t r0 = (int64_t)tile * kTileRows + tid;
-      const int64_t r1 = r0 + 128;
+      const int64_t r0 = (int64_t)tile * kTileRows + warp * kRowsPerWarp + lane;
 #pragma unroll
       for (int k = 0; k < kTcMaxKV; ++k) {
         if (k < p.kv) {
           const int64_t base = (int64_t)(p.flip_k ? p.kv - 1 - k : k) * p.n_out;
           tmp0[k] = r0 < p.n_out ? __ldg(p.nbr + base + r0) : -1;
-          tmp1[k] = r1 < p.n_out ? __ldg(p.nbr + base + r1) : -1;
         }
       }
     };
     auto park_table = [&]() {
+      __syncwarp();   // every lane has finished reading the previous tile's entries
 #pragma unroll
-      for (int k = 0; k < kTcMaxKV; ++k) {
-        if (k < p.kv) {
-          tbl[k * kTileRows] = tmp0[k];
-          tbl[k * kTileRows + 128] = tmp1[k];
-        }
-      }
+      for (int k = 0; k < kTcMaxKV; ++k)
+        if (k < p.kv) tbl[k * kTileRows] = tmp0[k];
+      __syncwarp();
     };
     load_table((int)blockIdx.x);
     park_table();
 
-    int s = 0;
+    // One gather instruction covers a few whole rows: lpr lanes copy the chunks of one row (contiguous in
+    // global memory, so a row costs one cache-line look-up instead of one per lane) and rpi = 32/lpr rows
+    // share the instruction.  A lane serves lpr consecutive rows of its warp's 32, so its table entries
+    // are adjacent in shared memory and come in with vector loads ahead of the copies.
+    const int lpr = p.kc < 8 ? p.kc : 8;          // lanes per row = rows per lane (kc is 2, 4, 8 or 16)
+    const int l_chunk = lane % lpr;
+    const int l_row0 = (lane / lpr) * lpr;        // first of this lane's rows inside the warp's 32
+    const int passes = p.kc / lpr;                // 2 only for 256-byte rows
+    const uint32_t lane_dst = (uint32_t)l_chunk * kRowsLbo + (uint32_t)(warp * kRowsPerWarp + l_row0) * 16u;
+    const int* tbl_row = s_tbl + warp * kRowsPerWarp + l_row0;
+    const uint8_t* rows_c = rows + l_chunk * 16;
+    const unsigned n_rows_u = (unsigned)p.n_rows;
+
+    int s = 0, arr_s = 0, issued = 0;
+    const int lag = S - 1 < 7 ? S - 1 : 7;   // stages a warp may run ahead of its landed copies
     uint32_t use = 0;
     bool bad = false, dead = false;
-    long long t_wait_empty = 0;
-    const long long t_begin = p.dbg_out ? clock64() : 0;
-    const uint32_t row_off = (uint32_t)tid * 16u;   // rows t and t+128: core-matrix offsets t*16 and t*16 + 2048
     for (int ti = 0; ti < my_tiles && !dead; ++ti) {
       const bool has_next = ti + 1 < my_tiles;
       if (has_next) load_table((int)blockIdx.x + (ti + 1) * (int)gridDim.x);
       for (int grp = 0; grp < groups; ++grp) {
-        const long long tw0 = p.dbg_out ? clock64() : 0;
-        if (!mbar_wait(smem_u32(&s_empty[s]), (use & 1u) ^ 1u, abort_flag)) { dead = true; break; }
-        if (p.dbg_out) t_wait_empty += clock64() - tw0;
+        // one lane polls (hundreds of threads polling and arriving on one mbarrier serialise on it)
+        bool ok_w = true;
+        if (lane == 0) ok_w = mbar_wait(smem_u32(&s_empty[s]), (use & 1u) ^ 1u, abort_flag, 32u);
+        if (__any_sync(0xffffffffu, !ok_w)) { dead = true; break; }   // also orders the other lanes behind the poll
         uint8_t* stage = stage0 + (size_t)s * stage_bytes;
         const int k0 = grp * GK;
         const int nk = min(GK, p.kv - k0);
@@ -193,79 +208,113 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
                    smem_u32(&s_full[s]));
         }
         for (int g = 0; g < nk; ++g) {
+          const int* trow = tbl_row + (k0 + g) * kTileRows;
+          const uint32_t dst0 = smem_u32(stage) + (uint32_t)(g * p.x_bytes) + lane_dst;
+          int r[8];
+          if (lpr == 8) {
+            const int4 a = *(const int4*)trow, b = *(const int4*)(trow + 4);
+            r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w; r[4] = b.x; r[5] = b.y; r[6] = b.z; r[7] = b.w;
+          } else if (lpr == 4) {
+            const int4 a = *(const int4*)trow;
+            r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
+          } else {
+            const int2 a = *(const int2*)trow;
+            r[0] = a.x; r[1] = a.y;
+          }
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            int in_row = tbl[(k0 + g) * kTileRows + 128 * h];
-            if (in_row >= p.n_rows) { bad = true; in_row = -1; }
-            const uint32_t ok = in_row >= 0 ? 16u : 0u;
-            const uint8_t* src = rows + (size_t)(in_row >= 0 ? in_row : 0) * p.row_bytes;
-            const uint32_t dst = smem_u32(stage) + (uint32_t)(g * p.x_bytes) + row_off + 2048u * h;
-            for (int c = 0; c < p.kc; ++c) cp_async_16(dst + (uint32_t)c * kRowsLbo, src + c * 16, ok);
+          for (int j = 0; j < 8; ++j) {
+            if (j < lpr) {
+              const bool present = (unsigned)r[j] < n_rows_u;       // false for -1 (absent) and for ids out of range
+              bad |= r[j] >= 0 && !present;
+              const uint8_t* src = rows_c + (size_t)(present ? r[j] : 0) * p.row_bytes;
+              const uint32_t dst = dst0 + (uint32_t)j * 16u;
+              if (!(p.debug & 1)) cp_async_16(dst, src, present ? 16u : 0u);
+              if (passes == 2) cp_async_16(dst + 8u * kRowsLbo, src + 128, present ? 16u : 0u);
+            }
           }
         }
-        cp_async_arrive_noinc(smem_u32(&s_full[s]));
+        // completion tracking: one commit group per stage; the stage issued `lag` iterations ago has landed
+        // once at most `lag` groups are pending, then one lane arrives for the whole warp
+        cp_async_commit();
+        if (issued >= lag) {
+          cp_async_wait_pending(lag);
+          fence_proxy_async();   // the copies were generic-proxy writes; the tensor core reads through the async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&s_full[arr_s]));
+          if (++arr_s == S) arr_s = 0;
+        }
+        ++issued;
         if (++s == S) { s = 0; ++use; }
       }
       if (has_next && !dead) park_table();
     }
-    if (p.dbg_out && tid == 0) {
-      p.dbg_out[blockIdx.x * 8 + 0] = t_wait_empty;
-      p.dbg_out[blockIdx.x * 8 + 4] = clock64() - t_begin;
+    cp_async_wait_pending(0);
+    fence_proxy_async();
+    __syncwarp();
+    if (!dead) {
+      const int pending = issued < lag ? issued : lag;
+      for (int j = 0; j < pending; ++j) {
+        if (lane == 0) mbar_arrive(smem_u32(&s_full[arr_s]));
+        if (++arr_s == S) arr_s = 0;
+      }
     }
     cp_async_wait_all();
     if (bad && p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
-  } else if (warp == 4) {
+  } else if (warp == kMmaWarp) {
     // ======================= MMA issuer =======================
     if (lane == 0) {
       const uint32_t idesc = p.is_i8 ? make_idesc(2u, 1u, 0u, 0u, (uint32_t)p.MP, kTileRows)
                                      : make_idesc(1u, p.is_bf16 ? 1u : 0u, 0u, 0u, (uint32_t)p.MP, kTileRows);
+      // This thread's instruction stream is the tensor pipe's feed: descriptors are kept as a constant high
+      // word plus a low word that only needs adds (start address and LBO live in the low 32 bits).
       const uint32_t lbo_w = (uint32_t)(p.MP / 8) * 128u;
+      const uint64_t w_desc0 = make_smem_desc(0u, lbo_w, 128u);
+      const uint64_t x_desc0 = make_smem_desc(0u, kRowsLbo, 128u);
+      const uint32_t w_hi = (uint32_t)(w_desc0 >> 32), w_lo0 = (uint32_t)w_desc0;
+      const uint32_t x_hi = (uint32_t)(x_desc0 >> 32), x_lo0 = (uint32_t)x_desc0;
+      const uint32_t w_step = (2u * lbo_w) >> 4, x_step = (2u * kRowsLbo) >> 4;   // two K chunks per instruction
       const int n_mma = p.kc / 2;  // 32 bytes of K per instruction (16 x 16-bit or 32 x 8-bit)
       bool dead = false;
       if (p.w_resident) dead = !mbar_wait(smem_u32(&s_w_full), 0u, abort_flag);
       int s = 0;
       uint32_t use = 0;
-      long long t_full = 0, t_acc = 0, t_issue = 0;
       for (int ti = 0; ti < my_tiles && !dead; ++ti) {
         const int buf = ti & 1;
-        const long long ta0 = p.dbg_out ? clock64() : 0;
         if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)ti >> 1) & 1u) ^ 1u, abort_flag)) break;
-        if (p.dbg_out) t_acc += clock64() - ta0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTileRows);
+        uint32_t accumulate = 0u;
+        int k = 0;
         for (int grp = 0; grp < groups; ++grp) {
-          const long long tf0 = p.dbg_out ? clock64() : 0;
           if (!mbar_wait(smem_u32(&s_full[s]), use & 1u, abort_flag)) { dead = true; break; }
-          const long long tf1 = p.dbg_out ? clock64() : 0;
           tc_fence_after();
-          const int k0 = grp * GK;
-          const int nk = min(GK, p.kv - k0);
+          const int nk = min(GK, p.kv - k);
           const uint32_t stage = smem_u32(stage0 + (size_t)s * stage_bytes);
+          uint32_t x_lo = x_lo0 + (stage >> 4);
+          uint32_t w_lo = w_lo0 + ((p.w_resident ? smem_u32(w_smem) + (uint32_t)(k * p.w_bytes)
+                                                 : stage + (uint32_t)(GK * p.x_bytes)) >> 4);
           for (int g = 0; g < nk; ++g) {
-            const uint32_t x_addr = stage + (uint32_t)(g * p.x_bytes);
-            const uint32_t w_addr = p.w_resident ? smem_u32(w_smem + (size_t)(k0 + g) * p.w_bytes)
-                                                 : stage + (uint32_t)(GK * p.x_bytes + g * p.w_bytes);
-            for (int j = 0; j < n_mma; ++j) {
-              const uint64_t a_desc = make_smem_desc(w_addr + (uint32_t)j * 2u * lbo_w, lbo_w, 128u);
-              const uint64_t b_desc = make_smem_desc(x_addr + (uint32_t)j * 2u * kRowsLbo, kRowsLbo, 128u);
-              const uint32_t accumulate = (k0 + g != 0 || j != 0) ? 1u : 0u;
-              if (p.is_i8) umma_i8(d_tmem, a_desc, b_desc, idesc, accumulate);
-              else umma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
+            uint32_t xl = x_lo, wl = w_lo;
+            if (p.is_i8) {
+              for (int j = 0; j < n_mma; ++j) {
+                umma_i8(d_tmem, ((uint64_t)w_hi << 32) | wl, ((uint64_t)x_hi << 32) | xl, idesc, accumulate);
+                accumulate = 1u; wl += w_step; xl += x_step;
+              }
+            } else {
+              for (int j = 0; j < n_mma; ++j) {
+                if (p.debug & 2) continue;
+                umma_f16(d_tmem, ((uint64_t)w_hi << 32) | wl, ((uint64_t)x_hi << 32) | xl, idesc, accumulate);
+                accumulate = 1u; wl += w_step; xl += x_step;
+              }
             }
+            x_lo += (uint32_t)p.x_bytes >> 4;
+            w_lo += (uint32_t)p.w_bytes >> 4;
           }
+          k += nk;
           umma_commit(smem_u32(&s_empty[s]));   // the slot is free once these MMAs have read it
-          if (p.dbg_out) {
-            t_full += tf1 - tf0;
-            t_issue += clock64() - tf1;
-          }
           if (++s == S) { s = 0; ++use; }
         }
         if (!dead) umma_commit(smem_u32(&s_acc_full[buf]));
-      }
-      if (p.dbg_out) {
-        p.dbg_out[blockIdx.x * 8 + 1] = t_full;
-        p.dbg_out[blockIdx.x * 8 + 2] = t_acc;
-        p.dbg_out[blockIdx.x * 8 + 6] = t_issue;
       }
     }
     __syncwarp();
@@ -279,17 +328,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     const float sc = (has_oc && p.scale) ? __ldg(p.scale + oc) : 1.f;
     const float bi = (has_oc && p.bias) ? __ldg(p.bias + oc) : 0.f;
     const int row_pitch = p.N * p.out_esize;      // bytes of one output row; the staging buffer uses the same pitch
-    long long t_epi_wait = 0;
     for (int ti = 0; ti < my_tiles; ++ti) {
       const int buf = ti & 1;
       const int64_t tile = (int64_t)blockIdx.x + (int64_t)ti * gridDim.x;
-      const long long te0 = p.dbg_out ? clock64() : 0;
-      const bool ok = mbar_wait(smem_u32(&s_acc_full[buf]), ((uint32_t)ti >> 1) & 1u, abort_flag);
-      if (p.dbg_out) t_epi_wait += clock64() - te0;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(smem_u32(&s_acc_full[buf]), ((uint32_t)ti >> 1) & 1u, abort_flag, 128u);
       if (__any_sync(0xffffffffu, !ok)) break;    // warp-uniform: tcgen05.ld is warp-wide
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTileRows);
-      for (int sub = 0; sub < kTileRows / kSubRows; ++sub) {
+      for (int sub = 0; sub < ((p.debug & 4) ? 0 : kTileRows / kSubRows); ++sub) {
         const int64_t row0 = tile * kTileRows + sub * kSubRows;
         if (row0 >= p.n_out) break;               // uniform over the four warps
         for (int c0 = 0; c0 < kSubRows; c0 += 16) {
@@ -321,7 +368,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_acc_empty[buf]));
     }
-    if (p.dbg_out && warp == 5 && lane == 0) p.dbg_out[blockIdx.x * 8 + 3] = t_epi_wait;
   }
 
   // ---- wind down: every thread arrives here, also after an abort
@@ -329,13 +375,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   __syncthreads();
   if (s_abort) {
     // let copies still in flight land before the CTA's shared memory is released
-    if (warp < 4) cp_async_wait_all();
+    if (warp < kProducerWarps) cp_async_wait_all();
     const long long t0 = clock64();
     while (clock64() - t0 < 4000000ll) { }
     if (tid == 0 && p.status) atomicOr(p.status, SPH_STATUS_TIMEOUT);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512u);
   }
@@ -363,7 +409,7 @@ bool tc_shape_ok(int dtype, int kv, int K, int N) {
   if (dtype != SPH_F16 && dtype != SPH_BF16 && dtype != SPH_I8) return false;
   const int e = dtype_bytes(dtype);
   const int row_bytes = K * e;
-  if (row_bytes % 32 != 0 || row_bytes < 32 || row_bytes > 256) return false;
+  if (row_bytes != 32 && row_bytes != 64 && row_bytes != 128 && row_bytes != 256) return false;
   if (N % 8 != 0 || N < 8 || N > 128) return false;
   if (kv < 1 || kv > kTcMaxKV) return false;
   return true;
@@ -385,7 +431,7 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
   p.MP = padded_m(N);
   p.row_bytes = K * dtype_bytes(dtype);
   p.kc = p.row_bytes / 16;
-  p.x_bytes = kTileRows * p.row_bytes;
+  p.x_bytes = p.kc * (int)kRowsLbo;   // kc chunk planes of 256 rows x 16 bytes (+ the bank skew)
   p.w_bytes = p.MP * p.row_bytes;
   p.flip_k = flip_k;
   p.is_i8 = dtype == SPH_I8;
@@ -400,7 +446,7 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
   off = (off + 1023) & ~1023;
   p.w_off = off;
   // offsets per stage: aim at 16 KB or more of gathered rows per stage so barrier traffic is amortised
-  int gk = 16384 / p.x_bytes;
+  int gk = 16640 / p.x_bytes;
   if (gk < 1) gk = 1;
   if (gk > 4) gk = 4;
   p.gk = gk;
@@ -416,10 +462,10 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
     return SPH_ERR_UNSUPPORTED;
   }
   {
+    const char* dbg = getenv("SPH_TC_DEBUG");
+    p.debug = dbg ? atoi(dbg) : 0;
     const char* st_env = getenv("SPH_TC_STAGES");
     if (st_env && atoi(st_env) >= 2 && atoi(st_env) <= stages) stages = atoi(st_env);
-    const char* dp = getenv("SPH_TC_DBGPTR");
-    p.dbg_out = dp ? (long long*)strtoull(dp, nullptr, 16) : nullptr;
   }
   p.stages = stages;
   const int smem_bytes = off + stages * stage_bytes;

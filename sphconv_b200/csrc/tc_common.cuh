@@ -46,22 +46,60 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of the phase (try_wait may suspend the thread for a system-dependent time).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 constexpr long long kWaitLimitCycles = 400ll * 1000ll * 1000ll;  // ~0.2 s of SM clocks: far beyond any healthy wait
 
 // Bounded wait.  `abort_flag` is a CTA-shared int: once any thread has timed out every later wait
 // returns at once.  Returns true when the phase completed.  The common case never reads a clock:
 // the bound is only armed after a burst of failed polls (reading %globaltimer costs about a microsecond,
 // which would serialise a pipeline that waits once per stage).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// `backoff_ns` > 0 makes a waiter that found the barrier not ready sleep between polls, so that warps
+// which are merely ahead of the pipeline do not take issue slots from the warp feeding the tensor pipe.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned backoff_ns = 0) {
 #pragma unroll 1
   for (int i = 0; i < 64; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns) __nanosleep(backoff_ns);
   }
   const long long t0 = clock64();
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
+      if (backoff_ns) __nanosleep(backoff_ns);
+    }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// Bounded busy-poll for the one thread whose latency feeds the tensor pipe: never suspends.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+  }
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 1024; ++i) {
+      if (mbar_test_wait(bar, parity)) return true;
     }
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
@@ -73,14 +111,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 
 // ---- copies ----------------------------------------------------------------------------------------
 // 16-byte async copy global -> shared; src_bytes == 0 writes zeros without touching global memory.
+// No "memory" clobber on purpose: volatile asm statements keep their order among themselves (barrier wait ->
+// copies -> arrive), while ordinary loads around them (the neighbour-table reads) stay free to be hoisted.
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
 }
 // The mbarrier receives one arrival once all cp.async issued so far by this thread have landed.
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Blocks until at most `n` of this thread's most recent commit groups are still in flight (n in 0..7).
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+  }
+}
 
 // Bulk (TMA engine, untiled) copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -116,8 +170,7 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
 }
 // int8 inputs, int32 accumulation.
 __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -125,8 +178,7 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
 }
 
 // 16 consecutive 32-bit columns of this thread's TMEM lane (lane = 32 * (warp % 4) + laneid).
