@@ -61,7 +61,6 @@ struct TcParams {
   int row_bytes;        // K * elem bytes
   int kc;               // 16-byte chunks per gathered row
   int stages;
-  int gk;               // kernel offsets gathered per pipeline stage
   int w_resident;       // all KV weight images live in shared memory
   int x_bytes, w_bytes; // per-offset operand bytes: gathered rows, weight image
   int flip_k;
@@ -74,21 +73,53 @@ struct TcParams {
   int* status;
   int num_tiles;
   int tbl_off, stg_off, w_off, stage_off;   // dynamic shared memory layout (byte offsets)
-  int debug;            // development switches (environment SPH_TC_DEBUG); 0 in normal use
 };
 
-__device__ __forceinline__ void stage_store(uint8_t* dst, int out_dtype, float v) {
+// 16 accumulator values of one output channel (16 consecutive output rows) -> the transpose buffer.
+// The dtype switch sits outside the element loop; `dst` points at (row 0 of the 16, this channel).
+template <bool I8>
+__device__ __forceinline__ void stage_store16(uint8_t* dst, int row_pitch, int out_dtype, const uint32_t (&raw)[16],
+                                              float sc, float bi, int relu) {
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float x = I8 ? (float)(int)raw[j] : __uint_as_float(raw[j]);
+    x = fmaf(x, sc, bi);
+    v[j] = relu ? fmaxf(x, 0.f) : x;
+  }
   switch (out_dtype) {
-    case SPH_F32: *(float*)dst = v; break;
-    case SPH_F16: *(__half*)dst = __float2half_rn(v); break;
-    case SPH_BF16: *(__nv_bfloat16*)dst = __float2bfloat16_rn(v); break;
-    default: *(int8_t*)dst = (int8_t)(int)fminf(fmaxf(rintf(v), -127.f), 127.f);
+    case SPH_F32:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) *(float*)(dst + j * row_pitch) = v[j];
+      break;
+    case SPH_F16:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) *(__half*)(dst + j * row_pitch) = __float2half_rn(v[j]);
+      break;
+    case SPH_BF16:
+#pragma unroll
+      for (int j = 0; j < 16; ++j) *(__nv_bfloat16*)(dst + j * row_pitch) = __float2bfloat16_rn(v[j]);
+      break;
+    default:
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        *(int8_t*)(dst + j * row_pitch) = (int8_t)(int)fminf(fmaxf(rintf(v[j]), -127.f), 127.f);
   }
 }
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// KC = 16-byte chunks per gathered row (2, 4, 8, 16), I8 = int8 operands.  Both are compile-time so that the
+// per-stage instruction streams of the gather warps and of the MMA thread have no loops or branches to
+// resolve: with two or three warps per scheduler nothing hides a lone warp's instruction latency, and those
+// streams, not the tensor pipe or the memory system, set the pace once the data path is asynchronous.
+template <int KC, bool I8>
 __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams p) {
+  constexpr int GK = KC == 2 ? 4 : KC == 4 ? 2 : 1;   // kernel offsets per pipeline stage
+  constexpr int LPR = KC < 8 ? KC : 8;           // lanes per row = rows per lane
+  constexpr int PASSES = KC / LPR;               // 2 only for 256-byte rows
+  constexpr int NMMA = KC / 2;                   // 32 bytes of K per instruction
+  constexpr uint32_t X_BYTES = (uint32_t)KC * kRowsLbo;
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ __align__(8) uint64_t s_full[kMaxStages];
   __shared__ __align__(8) uint64_t s_empty[kMaxStages];
@@ -102,8 +133,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int S = p.stages;
-  const int GK = p.gk;
-  const int stage_bytes = GK * (p.x_bytes + (p.w_resident ? 0 : p.w_bytes));
+  const int stage_bytes = GK * ((int)X_BYTES + (p.w_resident ? 0 : p.w_bytes));
   int* s_tbl = (int*)(smem + p.tbl_off);          // [kv][256] neighbour rows of the current tile
   uint8_t* s_stg = smem + p.stg_off;              // [64][N] epilogue transpose buffer
   uint8_t* w_smem = smem + p.w_off;               // resident weight images (if any)
@@ -113,7 +143,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(&s_full[s]), kProducerWarps + (p.w_resident ? 0 : 1));   // one arrival per gather warp
+      mbar_init(smem_u32(&s_full[s]), kProducerThreads + (p.w_resident ? 0 : 1));
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -173,146 +203,126 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     load_table((int)blockIdx.x);
     park_table();
 
-    // One gather instruction covers a few whole rows: lpr lanes copy the chunks of one row (contiguous in
-    // global memory, so a row costs one cache-line look-up instead of one per lane) and rpi = 32/lpr rows
-    // share the instruction.  A lane serves lpr consecutive rows of its warp's 32, so its table entries
-    // are adjacent in shared memory and come in with vector loads ahead of the copies.
-    const int lpr = p.kc < 8 ? p.kc : 8;          // lanes per row = rows per lane (kc is 2, 4, 8 or 16)
-    const int l_chunk = lane % lpr;
-    const int l_row0 = (lane / lpr) * lpr;        // first of this lane's rows inside the warp's 32
-    const int passes = p.kc / lpr;                // 2 only for 256-byte rows
+    // One gather instruction covers a few whole rows: LPR lanes copy the chunks of one row (contiguous in
+    // global memory, so a row costs one cache-line look-up instead of one per lane) and 32/LPR rows share
+    // the instruction.  A lane serves LPR consecutive rows of its warp's 32, so its table entries are
+    // adjacent in shared memory and come in with one or two vector loads ahead of the copies.
+    const int l_chunk = lane % LPR;
+    const int l_row0 = (lane / LPR) * LPR;        // first of this lane's rows inside the warp's 32
     const uint32_t lane_dst = (uint32_t)l_chunk * kRowsLbo + (uint32_t)(warp * kRowsPerWarp + l_row0) * 16u;
     const int* tbl_row = s_tbl + warp * kRowsPerWarp + l_row0;
     const uint8_t* rows_c = rows + l_chunk * 16;
     const unsigned n_rows_u = (unsigned)p.n_rows;
+    const uint32_t row_bytes = (uint32_t)KC * 16u;
+    const uint32_t stage0_u = smem_u32(stage0);
+    const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
 
-    int s = 0, arr_s = 0, issued = 0;
-    const int lag = S - 1 < 7 ? S - 1 : 7;   // stages a warp may run ahead of its landed copies
-    uint32_t use = 0;
-    bool bad = false, dead = false;
+    int s = 0;
+    uint32_t par = 1u;                            // parity to wait for on the empty barriers
+    uint32_t bad = 0u;
+    bool dead = false;
     for (int ti = 0; ti < my_tiles && !dead; ++ti) {
       const bool has_next = ti + 1 < my_tiles;
       if (has_next) load_table((int)blockIdx.x + (ti + 1) * (int)gridDim.x);
-      for (int grp = 0; grp < groups; ++grp) {
-        // one lane polls (hundreds of threads polling and arriving on one mbarrier serialise on it)
+      const int* trow = tbl_row;
+      for (int k0 = 0; k0 < p.kv; k0 += GK) {
+        // one lane polls: hundreds of threads polling one mbarrier serialise on it
         bool ok_w = true;
-        if (lane == 0) ok_w = mbar_wait(smem_u32(&s_empty[s]), (use & 1u) ^ 1u, abort_flag, 32u);
+        if (lane == 0) ok_w = mbar_wait(empty0 + 8u * s, par, abort_flag);
         if (__any_sync(0xffffffffu, !ok_w)) { dead = true; break; }   // also orders the other lanes behind the poll
-        uint8_t* stage = stage0 + (size_t)s * stage_bytes;
-        const int k0 = grp * GK;
-        const int nk = min(GK, p.kv - k0);
+        const uint32_t stage = stage0_u + (uint32_t)(s * stage_bytes);
         if (!p.w_resident && tid == 0) {
-          const uint32_t bytes = (uint32_t)(nk * p.w_bytes);
-          mbar_arrive_expect_tx(smem_u32(&s_full[s]), bytes);
-          bulk_g2s(smem_u32(stage + GK * p.x_bytes), (const uint8_t*)p.packed + (size_t)k0 * p.w_bytes, bytes,
-                   smem_u32(&s_full[s]));
+          const uint32_t bytes = (uint32_t)(min(GK, p.kv - k0) * p.w_bytes);
+          mbar_arrive_expect_tx(full0 + 8u * s, bytes);
+          bulk_g2s(stage + GK * X_BYTES, (const uint8_t*)p.packed + (size_t)k0 * p.w_bytes, bytes, full0 + 8u * s);
         }
-        for (int g = 0; g < nk; ++g) {
-          const int* trow = tbl_row + (k0 + g) * kTileRows;
-          const uint32_t dst0 = smem_u32(stage) + (uint32_t)(g * p.x_bytes) + lane_dst;
-          int r[8];
-          if (lpr == 8) {
-            const int4 a = *(const int4*)trow, b = *(const int4*)(trow + 4);
-            r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w; r[4] = b.x; r[5] = b.y; r[6] = b.z; r[7] = b.w;
-          } else if (lpr == 4) {
-            const int4 a = *(const int4*)trow;
-            r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
-          } else {
-            const int2 a = *(const int2*)trow;
-            r[0] = a.x; r[1] = a.y;
-          }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (j < lpr) {
-              const bool present = (unsigned)r[j] < n_rows_u;       // false for -1 (absent) and for ids out of range
-              bad |= r[j] >= 0 && !present;
-              const uint8_t* src = rows_c + (size_t)(present ? r[j] : 0) * p.row_bytes;
-              const uint32_t dst = dst0 + (uint32_t)j * 16u;
-              if (!(p.debug & 1)) cp_async_16(dst, src, present ? 16u : 0u);
-              if (passes == 2) cp_async_16(dst + 8u * kRowsLbo, src + 128, present ? 16u : 0u);
+        for (int g = 0; g < GK; ++g) {
+          if (GK == 1 || k0 + g < p.kv) {
+            int r[LPR];
+            if (LPR == 8) {
+              const int4 a = *(const int4*)trow, b = *(const int4*)(trow + 4);
+              r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
+              r[4 % LPR] = b.x; r[5 % LPR] = b.y; r[6 % LPR] = b.z; r[7 % LPR] = b.w;
+            } else if (LPR == 4) {
+              const int4 a = *(const int4*)trow;
+              r[0] = a.x; r[1] = a.y; r[2 % LPR] = a.z; r[3 % LPR] = a.w;
+            } else {
+              const int2 a = *(const int2*)trow;
+              r[0] = a.x; r[1] = a.y;
             }
+            const uint32_t dst0 = stage + (uint32_t)g * X_BYTES + lane_dst;
+#pragma unroll
+            for (int j = 0; j < LPR; ++j) {
+              const bool present = (unsigned)r[j] < n_rows_u;     // false for -1 (absent) and for ids out of range
+              bad |= (uint32_t)(r[j] + 1) & (present ? 0u : ~0u);  // non-zero only for an id that is neither -1 nor valid
+              const uint8_t* src = rows_c + (size_t)(present ? (uint32_t)r[j] : 0u) * row_bytes;
+              const uint32_t sz = present ? 16u : 0u;
+              cp_async_16(dst0 + (uint32_t)j * 16u, src, sz);
+              if (PASSES == 2) cp_async_16(dst0 + (uint32_t)j * 16u + 8u * kRowsLbo, src + 128, sz);
+            }
+            trow += kTileRows;
           }
         }
-        // completion tracking: one commit group per stage; the stage issued `lag` iterations ago has landed
-        // once at most `lag` groups are pending, then one lane arrives for the whole warp
-        cp_async_commit();
-        if (issued >= lag) {
-          cp_async_wait_pending(lag);
-          fence_proxy_async();   // the copies were generic-proxy writes; the tensor core reads through the async proxy
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&s_full[arr_s]));
-          if (++arr_s == S) arr_s = 0;
-        }
-        ++issued;
-        if (++s == S) { s = 0; ++use; }
+        cp_async_arrive_noinc(full0 + 8u * s);
+        if (++s == S) { s = 0; par ^= 1u; }
       }
       if (has_next && !dead) park_table();
-    }
-    cp_async_wait_pending(0);
-    fence_proxy_async();
-    __syncwarp();
-    if (!dead) {
-      const int pending = issued < lag ? issued : lag;
-      for (int j = 0; j < pending; ++j) {
-        if (lane == 0) mbar_arrive(smem_u32(&s_full[arr_s]));
-        if (++arr_s == S) arr_s = 0;
-      }
     }
     cp_async_wait_all();
     if (bad && p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
   } else if (warp == kMmaWarp) {
     // ======================= MMA issuer =======================
     if (lane == 0) {
-      const uint32_t idesc = p.is_i8 ? make_idesc(2u, 1u, 0u, 0u, (uint32_t)p.MP, kTileRows)
-                                     : make_idesc(1u, p.is_bf16 ? 1u : 0u, 0u, 0u, (uint32_t)p.MP, kTileRows);
-      // This thread's instruction stream is the tensor pipe's feed: descriptors are kept as a constant high
-      // word plus a low word that only needs adds (start address and LBO live in the low 32 bits).
+      const uint32_t idesc = I8 ? make_idesc(2u, 1u, 0u, 0u, (uint32_t)p.MP, kTileRows)
+                                : make_idesc(1u, p.is_bf16 ? 1u : 0u, 0u, 0u, (uint32_t)p.MP, kTileRows);
+      // Descriptors are a constant high word plus a low word that only needs adds (start address and LBO
+      // live in the low 32 bits, in 16-byte units).
       const uint32_t lbo_w = (uint32_t)(p.MP / 8) * 128u;
       const uint64_t w_desc0 = make_smem_desc(0u, lbo_w, 128u);
       const uint64_t x_desc0 = make_smem_desc(0u, kRowsLbo, 128u);
-      const uint32_t w_hi = (uint32_t)(w_desc0 >> 32), w_lo0 = (uint32_t)w_desc0;
-      const uint32_t x_hi = (uint32_t)(x_desc0 >> 32), x_lo0 = (uint32_t)x_desc0;
-      const uint32_t w_step = (2u * lbo_w) >> 4, x_step = (2u * kRowsLbo) >> 4;   // two K chunks per instruction
-      const int n_mma = p.kc / 2;  // 32 bytes of K per instruction (16 x 16-bit or 32 x 8-bit)
+      const uint64_t w_hi = w_desc0 & 0xffffffff00000000ull, x_hi = x_desc0 & 0xffffffff00000000ull;
+      const uint32_t w_step = (2u * lbo_w) >> 4;                 // two K chunks per instruction
+      constexpr uint32_t x_step = (2u * kRowsLbo) >> 4;
+      const uint32_t w_units = (uint32_t)p.w_bytes >> 4;
+      const uint32_t stage_units = (uint32_t)stage_bytes >> 4;
+      const uint32_t x_lo_first = (uint32_t)x_desc0 + (smem_u32(stage0) >> 4);
+      const uint32_t w_lo_res = (uint32_t)w_desc0 + (smem_u32(w_smem) >> 4);          // resident images
+      const uint32_t w_in_stage = (uint32_t)w_desc0 - (uint32_t)x_desc0 + ((GK * X_BYTES) >> 4);   // streamed: behind the rows
+      const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
       bool dead = false;
       if (p.w_resident) dead = !mbar_wait(smem_u32(&s_w_full), 0u, abort_flag);
       int s = 0;
-      uint32_t use = 0;
+      uint32_t par = 0u;                                          // parity to wait for on the full barriers
+      uint32_t x_lo = x_lo_first;
       for (int ti = 0; ti < my_tiles && !dead; ++ti) {
         const int buf = ti & 1;
         if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)ti >> 1) & 1u) ^ 1u, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTileRows);
         uint32_t accumulate = 0u;
-        int k = 0;
-        for (int grp = 0; grp < groups; ++grp) {
-          if (!mbar_wait(smem_u32(&s_full[s]), use & 1u, abort_flag)) { dead = true; break; }
+        uint32_t w_lo = w_lo_res;
+        for (int k0 = 0; k0 < p.kv; k0 += GK) {
+          if (!mbar_wait(full0 + 8u * s, par, abort_flag)) { dead = true; break; }
           tc_fence_after();
-          const int nk = min(GK, p.kv - k);
-          const uint32_t stage = smem_u32(stage0 + (size_t)s * stage_bytes);
-          uint32_t x_lo = x_lo0 + (stage >> 4);
-          uint32_t w_lo = w_lo0 + ((p.w_resident ? smem_u32(w_smem) + (uint32_t)(k * p.w_bytes)
-                                                 : stage + (uint32_t)(GK * p.x_bytes)) >> 4);
-          for (int g = 0; g < nk; ++g) {
-            uint32_t xl = x_lo, wl = w_lo;
-            if (p.is_i8) {
-              for (int j = 0; j < n_mma; ++j) {
-                umma_i8(d_tmem, ((uint64_t)w_hi << 32) | wl, ((uint64_t)x_hi << 32) | xl, idesc, accumulate);
-                accumulate = 1u; wl += w_step; xl += x_step;
-              }
-            } else {
-              for (int j = 0; j < n_mma; ++j) {
-                if (p.debug & 2) continue;
-                umma_f16(d_tmem, ((uint64_t)w_hi << 32) | wl, ((uint64_t)x_hi << 32) | xl, idesc, accumulate);
-                accumulate = 1u; wl += w_step; xl += x_step;
+          const uint32_t wl0 = p.w_resident ? w_lo : x_lo + w_in_stage;
+#pragma unroll
+          for (int g = 0; g < GK; ++g) {
+            if (GK == 1 || k0 + g < p.kv) {
+#pragma unroll
+              for (int j = 0; j < NMMA; ++j) {
+                const uint64_t wd = w_hi | (uint64_t)(wl0 + (uint32_t)g * w_units + (uint32_t)j * w_step);
+                const uint64_t xd = x_hi | (uint64_t)(x_lo + (uint32_t)g * (X_BYTES >> 4) + (uint32_t)j * x_step);
+                if (I8) umma_i8(d_tmem, wd, xd, idesc, accumulate);
+                else umma_f16(d_tmem, wd, xd, idesc, accumulate);
+                accumulate = 1u;
               }
             }
-            x_lo += (uint32_t)p.x_bytes >> 4;
-            w_lo += (uint32_t)p.w_bytes >> 4;
           }
-          k += nk;
-          umma_commit(smem_u32(&s_empty[s]));   // the slot is free once these MMAs have read it
-          if (++s == S) { s = 0; ++use; }
+          umma_commit(empty0 + 8u * s);          // the slot is free once these MMAs have read it
+          w_lo += GK * w_units;
+          x_lo += stage_units;
+          if (++s == S) { s = 0; par ^= 1u; x_lo = x_lo_first; }
         }
         if (!dead) umma_commit(smem_u32(&s_acc_full[buf]));
       }
@@ -336,22 +346,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       if (__any_sync(0xffffffffu, !ok)) break;    // warp-uniform: tcgen05.ld is warp-wide
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTileRows);
-      for (int sub = 0; sub < ((p.debug & 4) ? 0 : kTileRows / kSubRows); ++sub) {
+      for (int sub = 0; sub < kTileRows / kSubRows; ++sub) {
         const int64_t row0 = tile * kTileRows + sub * kSubRows;
         if (row0 >= p.n_out) break;               // uniform over the four warps
         for (int c0 = 0; c0 < kSubRows; c0 += 16) {
           uint32_t raw[16];
           tmem_ld16(taddr + (uint32_t)(sub * kSubRows + c0), raw);
           tmem_ld_wait();
-          if (has_oc) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float x = p.is_i8 ? (float)(int)raw[j] : __uint_as_float(raw[j]);
-              x = x * sc + bi;
-              if (p.relu) x = fmaxf(x, 0.f);
-              stage_store(s_stg + (c0 + j) * row_pitch + oc * p.out_esize, p.out_dtype, x);
-            }
-          }
+          if (has_oc)
+            stage_store16<I8>(s_stg + c0 * row_pitch + oc * p.out_esize, row_pitch, p.out_dtype, raw, sc, bi, p.relu);
         }
         epilogue_bar();
         // the 64 rows are one contiguous range of the output: copy it out with 16-byte stores
@@ -405,14 +408,50 @@ __global__ void pack_weight_kernel(const T* __restrict__ w, int kv, int K, int N
 
 int padded_m(int N) { return N <= 64 ? 64 : 128; }
 
+// Dynamic shared-memory layout: neighbour table, epilogue transpose buffer, (resident weights), stages.
+// Fills the layout fields of p; false when two stages do not fit.
+bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
+  int off = 0;
+  p->tbl_off = off; off += kv * kTileRows * (int)sizeof(int);
+  p->stg_off = off; off += kSubRows * p->N * p->out_esize;
+  off = (off + 1023) & ~1023;
+  p->w_off = off;
+  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? 2 : 1;   // kernel offsets per stage (must match the kernel's GK)
+  const int w_all = kv * p->w_bytes;
+  p->w_resident = (off + w_all + 2 * gk * p->x_bytes <= kSmemTotal) ? 1 : 0;
+  if (p->w_resident) off += w_all;
+  p->stage_off = off;
+  const int stage_bytes = gk * (p->x_bytes + (p->w_resident ? 0 : p->w_bytes));
+  int stages = (kSmemTotal - off) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return false;
+  const char* st_env = getenv("SPH_TC_STAGES");
+  if (st_env && atoi(st_env) >= 2 && atoi(st_env) <= stages) stages = atoi(st_env);
+  p->stages = stages;
+  *smem_bytes = off + stages * stage_bytes;
+  return true;
+}
+
+void fill_shape(TcParams* p, int dtype, int K, int N, int out_esize) {
+  p->K = K; p->N = N;
+  p->MP = padded_m(N);
+  p->row_bytes = K * dtype_bytes(dtype);
+  p->kc = p->row_bytes / 16;
+  p->x_bytes = p->kc * (int)kRowsLbo;   // kc chunk planes of 256 rows x 16 bytes (+ the bank skew)
+  p->w_bytes = p->MP * p->row_bytes;
+  p->out_esize = out_esize;
+}
+
 bool tc_shape_ok(int dtype, int kv, int K, int N) {
   if (dtype != SPH_F16 && dtype != SPH_BF16 && dtype != SPH_I8) return false;
-  const int e = dtype_bytes(dtype);
-  const int row_bytes = K * e;
+  const int row_bytes = K * dtype_bytes(dtype);
   if (row_bytes != 32 && row_bytes != 64 && row_bytes != 128 && row_bytes != 256) return false;
   if (N % 8 != 0 || N < 8 || N > 128) return false;
   if (kv < 1 || kv > kTcMaxKV) return false;
-  return true;
+  TcParams p;
+  fill_shape(&p, dtype, K, N, 4);   // widest output element
+  int bytes = 0;
+  return plan_smem(&p, kv, &bytes);
 }
 
 }  // namespace
@@ -427,60 +466,50 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
   TcParams p;
   p.rows = rows; p.packed = packed; p.nbr = nbr;
   p.n_rows = n_rows; p.n_out = n_out;
-  p.kv = kv; p.K = K; p.N = N;
-  p.MP = padded_m(N);
-  p.row_bytes = K * dtype_bytes(dtype);
-  p.kc = p.row_bytes / 16;
-  p.x_bytes = p.kc * (int)kRowsLbo;   // kc chunk planes of 256 rows x 16 bytes (+ the bank skew)
-  p.w_bytes = p.MP * p.row_bytes;
+  p.kv = kv;
+  fill_shape(&p, dtype, K, N, dtype_bytes(out_dtype));
   p.flip_k = flip_k;
   p.is_i8 = dtype == SPH_I8;
   p.is_bf16 = dtype == SPH_BF16;
   p.scale = scale; p.bias = bias; p.relu = relu;
-  p.out = out; p.out_dtype = out_dtype; p.out_esize = dtype_bytes(out_dtype); p.status = status;
+  p.out = out; p.out_dtype = out_dtype; p.status = status;
   p.num_tiles = (int)div_up64(n_out, kTileRows);
-  // dynamic shared memory: neighbour table, epilogue transpose buffer, (resident weights), stages
-  int off = 0;
-  p.tbl_off = off; off += kv * kTileRows * (int)sizeof(int);
-  p.stg_off = off; off += kSubRows * N * p.out_esize;
-  off = (off + 1023) & ~1023;
-  p.w_off = off;
-  // offsets per stage: aim at 16 KB or more of gathered rows per stage so barrier traffic is amortised
-  int gk = 16640 / p.x_bytes;
-  if (gk < 1) gk = 1;
-  if (gk > 4) gk = 4;
-  p.gk = gk;
-  const int w_all = kv * p.w_bytes;
-  p.w_resident = (off + w_all + 4 * gk * p.x_bytes <= kSmemTotal) ? 1 : 0;
-  if (p.w_resident) off += w_all;
-  p.stage_off = off;
-  const int stage_bytes = gk * (p.x_bytes + (p.w_resident ? 0 : p.w_bytes));
-  int stages = (kSmemTotal - off) / stage_bytes;
-  if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2) {
+  int smem_bytes = 0;
+  if (!plan_smem(&p, kv, &smem_bytes)) {
     set_error("conv_gather_tc: operands do not fit in shared memory");
     return SPH_ERR_UNSUPPORTED;
   }
-  {
-    const char* dbg = getenv("SPH_TC_DEBUG");
-    p.debug = dbg ? atoi(dbg) : 0;
-    const char* st_env = getenv("SPH_TC_STAGES");
-    if (st_env && atoi(st_env) >= 2 && atoi(st_env) <= stages) stages = atoi(st_env);
-  }
-  p.stages = stages;
-  const int smem_bytes = off + stages * stage_bytes;
-
   static int s_sms = 0;
   if (s_sms == 0) {
     int dev = 0;
     SPH_CUDA(cudaGetDevice(&dev));
     SPH_CUDA(cudaDeviceGetAttribute(&s_sms, cudaDevAttrMultiProcessorCount, dev));
   }
-  SPH_CUDA(cudaFuncSetAttribute(conv_gather_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   // every CTA takes all 512 TMEM columns, so exactly one is resident per SM
   int grid = s_sms < p.num_tiles ? s_sms : p.num_tiles;
   if (grid < 1) return SPH_OK;
-  conv_gather_tc_kernel<<<grid, kTcThreads, smem_bytes, st>>>(p);
+#define SPH_TC_LAUNCH(KC_, I8_)                                                                                  \
+  do {                                                                                                         \
+    SPH_CUDA(cudaFuncSetAttribute(conv_gather_tc_kernel<KC_, I8_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                  smem_bytes));                                                                \
+    conv_gather_tc_kernel<KC_, I8_><<<grid, kTcThreads, smem_bytes, st>>>(p);                                  \
+  } while (0)
+  if (p.is_i8) {
+    switch (p.kc) {
+      case 2: SPH_TC_LAUNCH(2, true); break;
+      case 4: SPH_TC_LAUNCH(4, true); break;
+      case 8: SPH_TC_LAUNCH(8, true); break;
+      default: SPH_TC_LAUNCH(16, true); break;
+    }
+  } else {
+    switch (p.kc) {
+      case 2: SPH_TC_LAUNCH(2, false); break;
+      case 4: SPH_TC_LAUNCH(4, false); break;
+      case 8: SPH_TC_LAUNCH(8, false); break;
+      default: SPH_TC_LAUNCH(16, false); break;
+    }
+  }
+#undef SPH_TC_LAUNCH
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
