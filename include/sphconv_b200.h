@@ -85,6 +85,24 @@ int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, 
                    void* d_scratch, int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int32_t* d_nbr,
                    int fill_unused, int32_t* d_status, void* stream);
 
+/* Same operation as sph_rules_subm, for callers that must not allocate device memory: plug-ins running inside
+ * a host application that owns the allocator, code between cudaStreamBeginCapture / EndCapture, real-time loops
+ * with a no-malloc rule, or language runtimes whose buffers cannot be handed out as scratch.  It has no
+ * counterpart in the reference (whose ops allocate freely through ATen).  The scratch (the per-column depth
+ * index built for inputs with long columns) is a fixed array inside the library of
+ * SPH_RULES_SUBM_STATIC_SCRATCH_BYTES bytes; every device that loads the library keeps that much memory
+ * reserved until the process exits.  Inputs that would need more are rejected with SPH_ERR_LIMIT and a
+ * message naming both sizes (sph_rules_subm_scratch_bytes() tells the need in advance).  The function never
+ * calls cudaMalloc / cudaFree or any allocating routine.
+ *  - The first call on each device looks up the array's device address; make that call outside of any stream
+ *    capture, with the device current.
+ *  - All calls on a device share the one array: the index is cleared and rebuilt by every call, and two calls
+ *    whose kernels can overlap on the GPU (different streams, no ordering between them) race on it. */
+#define SPH_RULES_SUBM_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int sph_rules_subm_static(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
+                          int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int32_t* d_nbr,
+                          int fill_unused, int32_t* d_status, void* stream);
+
 /* Strided ("regular") sparse conv, step 1: output sparsity pattern.
  * ref: get_rules, src/sphconv/rules.cu:405-462 (prepareGridKernel + the cumsum/roll scans).
  *   d_scratch   sph_rules_strided_scratch_bytes(g, nnz) bytes; must be kept untouched until step 2 has run

@@ -40,6 +40,7 @@ SIGNATURES = {
     "sph_num_tiles": (cint, [ctypes.POINTER(Geom)]),
     "sph_rules_subm_scratch_bytes": (i64, [ctypes.POINTER(Geom), i64]),
     "sph_rules_subm": (cint, [vp, vp, i64, ctypes.POINTER(Geom), vp, i32, vp, vp, vp, cint, vp, vp]),
+    "sph_rules_subm_static": (cint, [vp, vp, i64, ctypes.POINTER(Geom), i32, vp, vp, vp, cint, vp, vp]),
     "sph_rules_strided_scratch_bytes": (i64, [ctypes.POINTER(Geom), i64]),
     "sph_rules_strided_count": (cint, [vp, vp, i64, ctypes.POINTER(Geom), vp, vp, vp, c_i32p, vp]),
     "sph_rules_strided_fill": (cint, [vp, vp, i64, ctypes.POINTER(Geom), vp, vp, i64, i32, vp, vp, vp, vp, vp, cint,

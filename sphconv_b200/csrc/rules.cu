@@ -557,6 +557,43 @@ extern "C" int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, in
                      nullptr, cm, fill_unused, d_status, (cudaStream_t)stream);
 }
 
+// ---- allocation-free variant of sph_rules_subm ---------------------------------------------------
+// The scratch of the submanifold rule kernel (the per-column depth-bitmask index) lives in a fixed
+// device array instead of caller memory.  The array's name is only a host-side handle: the kernels need
+// its device address, looked up once per device with cudaGetSymbolAddress while that device is current.
+static __device__ __align__(256) unsigned char g_subm_static_scratch[SPH_RULES_SUBM_STATIC_SCRATCH_BYTES];
+
+extern "C" int sph_rules_subm_static(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz,
+                                     const sph_geom* s, int32_t tile_n_max, int32_t* d_rules,
+                                     int32_t* d_rule_size, int32_t* d_nbr, int fill_unused, int32_t* d_status,
+                                     void* stream) {
+  constexpr int kMaxDevices = 64;
+  static void* s_addr[kMaxDevices] = {nullptr};
+  Geom g;
+  int rc = make_geom(s, &g);
+  if (rc != SPH_OK) return rc;
+  const size_t need = colmask_bytes(g, nnz);
+  if (need > (size_t)SPH_RULES_SUBM_STATIC_SCRATCH_BYTES) {
+    set_error("sph_rules_subm_static: this input needs %zu bytes of scratch, the built-in buffer holds %d; "
+              "use sph_rules_subm with caller-provided scratch", need, (int)SPH_RULES_SUBM_STATIC_SCRATCH_BYTES);
+    return SPH_ERR_LIMIT;
+  }
+  int dev = 0;
+  SPH_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error("sph_rules_subm_static: device ordinal %d not supported", dev);
+    return SPH_ERR_LIMIT;
+  }
+  if (s_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    SPH_CUDA(cudaGetSymbolAddress(&ptr, g_subm_static_scratch));
+    s_addr[dev] = ptr;
+  }
+  // the index is rebuilt (cleared first) by every call; nothing is carried over from the previous one
+  return sph_rules_subm(d_z_idx, d_z_ptr, nnz, s, s_addr[dev], tile_n_max, d_rules, d_rule_size, d_nbr, fill_unused,
+                        d_status, stream);
+}
+
 namespace {
 struct StridedScratch {
   int words;
