@@ -86,8 +86,8 @@ int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, 
                    int fill_unused, int32_t* d_status, void* stream);
 
 /* Same operation as sph_rules_subm, for callers that must not allocate device memory: plug-ins running inside
- * a host application that owns the allocator, code between cudaStreamBeginCapture / EndCapture, real-time loops
- * with a no-malloc rule, or language runtimes whose buffers cannot be handed out as scratch.  It has no
+ * a host application that owns the allocator, real-time loops with a no-malloc rule, or language runtimes
+ * whose buffers cannot be handed out as scratch.  It has no
  * counterpart in the reference (whose ops allocate freely through ATen).  The scratch (the per-column depth
  * index built for inputs with long columns) is a fixed array inside the library of
  * SPH_RULES_SUBM_STATIC_SCRATCH_BYTES bytes; every device that loads the library keeps that much memory
