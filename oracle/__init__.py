@@ -16,8 +16,10 @@ What it restates (paths are relative to the reference project):
 
 Pinning.  The reference holds no golden vectors or known-answer files for this path (its tests
 compute every expectation at run time with spconv 1.x or dense torch conv3d) and has no CPU
-implementation.  The oracle is therefore pinned two ways: (1) against the dense-conv3d construction
-of the reference's tests, on CPU, for occupancy, forward, dgrad and wgrad; (2) against outputs of the
-reference's own CUDA kernels (``oracle/_ref``, built from the unmodified reference sources by
-``oracle/build_ref.py``) recorded on a B200 into ``tests/golden/`` by ``tests/golden/make_golden.py``.
+implementation.  The oracle is pinned two ways: (1) ``tests/test_oracle.py`` checks it against the
+dense-conv3d construction of the reference's tests, on CPU, for occupancy, forward, dgrad and wgrad;
+(2) ``tests/test_golden.py`` checks it against outputs of the reference's own CUDA kernels
+(``oracle/_ref``, built from the unmodified reference sources by ``oracle/build_ref.py``) recorded on a
+B200 into ``tests/golden/`` by ``tests/golden/make_golden.py``: rule sizes, pair sets, output indices,
+and fp32 forward / dgrad / wgrad.
 """

@@ -4,7 +4,7 @@ Sources are compiled where they lie in the reference tree (REFERENCE_ROOT, defau
 src/sphconv/rules.cu and src/sphconv/tensor.cu unmodified, plus - when a CUTLASS header tree is found -
 src/sphconv/rule_conv.cu.  The reference pins no CUTLASS version (its submodule directory is empty); the
 only copy on this machine is a 4.x tree whose MmaPipelined calls `iterator.clear_mask(bool)`, so the build
-puts a temporary copy of include/sphconv/iterator.cu.h with that one signature widened on the include path
+puts a temporary copy of include/sphconv/iterator.cu.h with that one method taking the flag on the include path
 (the temporary copy is deleted afterwards; nothing of the reference is stored in this repository).
 
     python -m oracle.build_ref            # builds if the reference tree is present, else does nothing
@@ -60,7 +60,11 @@ def build(with_conv=True, verbose=False):
             shim = os.path.join(tmp, "shim", "sphconv")
             os.makedirs(shim)
             text = open(os.path.join(ref, "include/sphconv/iterator.cu.h")).read()
-            text = re.sub(r"void\s+clear_mask\s*\(\s*\)", "void clear_mask(bool enable = true)", text)
+            # CUTLASS 2.x called `if (k_iterations <= 1) it.clear_mask();`, 4.x calls `it.clear_mask(k_iterations <= 1)`:
+            # same behaviour needs the flag to guard the body
+            text, n_sub = re.subn(r"void\s+clear_mask\s*\(\s*\)\s*\{",
+                                  "void clear_mask(bool enable = true)\n    {\n        if (!enable) return;", text)
+            assert n_sub == 6, "unexpected number of clear_mask definitions: %d" % n_sub
             open(os.path.join(shim, "iterator.cu.h"), "w").write(text)
             sources.append((os.path.join(ref, "src/sphconv/rule_conv.cu"),
                             ["-I" + os.path.join(tmp, "shim"), "-I" + cutlass]))
