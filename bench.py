@@ -2,7 +2,7 @@
 """Benchmark of the sphconv hot path on B200: rule generation + rule-driven sparse convolution of the
 SECOND-style 8-layer encoder over synthetic range-voxel scans.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg5|cfg4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg4|cfg5] [--impl reference]
 
 One step = one pass of the whole path over one batch of scans: five rule sets (the SubM pairs share
 theirs) and eight convolutions.  Rank r of N processes its own scans (no data-path collective).
@@ -89,14 +89,15 @@ class ClockSampler:
 
 
 def workload(name, world, rank, batch_override):
+    """(config, scans per forward pass, forward passes per step, scaling, first scan id of this rank)."""
     cfg = dict(synthetic.CONFIGS[name])
-    if name == "cfg5":          # 64 scans sharded over the ranks (fixed total work)
-        B = batch_override or max(1, 64 // world)
-        scaling = "strong"
-    else:                       # every rank runs the configuration's batch (fixed per-GPU work)
-        B = batch_override or cfg["B"]
-        scaling = "weak"
-    return cfg, B, scaling, rank * B
+    if name == "cfg5":          # 64 scans sharded over the ranks (fixed total work), run 8 scans at a time
+        per_rank = batch_override or max(1, 64 // world)
+        B = min(8, per_rank)
+        chunks = max(1, per_rank // B)
+        return cfg, B, chunks, "strong", rank * B * chunks
+    B = batch_override or cfg["B"]   # every rank runs the configuration's batch (fixed per-GPU work)
+    return cfg, B, 1, "weak", rank * B
 
 
 def cpu_dense_scan(cfg, scan_id, threads, w_div=1):
@@ -155,7 +156,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg3", choices=["cfg3"])
+    ap.add_argument("--workload", default="cfg3", choices=["cfg3", "cfg4", "cfg5"])
     ap.add_argument("--batch", type=int, default=0, help="scans per rank per step (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -180,34 +181,75 @@ def main():
     from sphconv_b200 import _capi, profiling
     from sphconv_b200.encoder import build_encoder8
 
-    cfg, B, scaling, first_scan = workload(args.workload, world, rank, args.batch)
-    dtype_name = {"cfg3": "fp16", "cfg4": "bf16", "cfg5": "fp16"}[args.workload]
-    dtype = DTYPES[dtype_name]
+    from sphconv_b200 import quant, sharding
+    cfg, B, chunks, scaling, first_scan = workload(args.workload, world, rank, args.batch)
+    dtype_name = {"cfg3": "fp16", "cfg4": "bf16", "cfg5": "int8"}[args.workload]
+    training = args.workload == "cfg4"
     shape = cfg["shape"]
-    batch = synthetic.make_batch(cfg, batch=B, first_scan=first_scan)
-    h_feat = torch.as_tensor(batch["feature"]).to(dtype).pin_memory()
-    h_zidx = torch.as_tensor(batch["z_idx"]).pin_memory()
-    h_zptr = torch.as_tensor(batch["z_ptr"]).pin_memory()
-    d_feat, d_zidx, d_zptr = h_feat.to(dev), h_zidx.to(dev), h_zptr.to(dev)
-    net = build_encoder8(dtype=dtype, device=dev, fused=True).eval()
     sphconv.config.fill_unused_rules = False   # entries of `rules` past rule_size are never read by the path
     lib = _capi.lib()
+    h_in, d_in = [], []
+    if args.workload == "cfg5":
+        net32 = build_encoder8(dtype=torch.float32, device=dev, fused=True).eval()
+        cb = synthetic.make_batch(cfg, batch=1, first_scan=10_000)
+        with torch.no_grad():
+            net = quant.quantize_encoder(net32, sphconv.SparseConvTensor(
+                torch.as_tensor(cb["feature"], device=dev), shape, 1, z_idx=torch.as_tensor(cb["z_idx"], device=dev),
+                z_ptr=torch.as_tensor(cb["z_ptr"], device=dev)))
+        del net32
+        torch.cuda.empty_cache()
+        feat_dtype = torch.int8
+    else:
+        feat_dtype = DTYPES[dtype_name]
+        net = build_encoder8(dtype=feat_dtype, device=dev, fused=True)
+        net = net.train() if training else net.eval()
+    for c in range(chunks):
+        batch = synthetic.make_batch(cfg, batch=B, first_scan=first_scan + c * B)
+        f = torch.as_tensor(batch["feature"])
+        f = net.quantize_input(f.to(dev)).cpu() if args.workload == "cfg5" else f.to(feat_dtype)
+        h = (f.pin_memory(), torch.as_tensor(batch["z_idx"]).pin_memory(), torch.as_tensor(batch["z_ptr"]).pin_memory())
+        h_in.append(h)
+        d_in.append(tuple(t.to(dev) for t in h))
+    params = list(net.parameters()) if training else []
+    grad_out = {}
+
+    def run_pass(f, zi, zp):
+        if not training:
+            return net(sphconv.SparseConvTensor(f, shape, B, z_idx=zi, z_ptr=zp))
+        # cfg4: forward + dgrad + wgrad of every layer, then ONE all-reduce of the flat fp32 weight gradient
+        for p_ in params:
+            p_.grad = None
+        x = sphconv.SparseConvTensor(f.detach().requires_grad_(True), shape, B, z_idx=zi, z_ptr=zp)
+        y = net(x)
+        n = y.feature.shape[0]
+        if grad_out.get("n") != n:
+            g = torch.Generator(device=dev).manual_seed(4)
+            grad_out["g"] = torch.randn(y.feature.shape, generator=g, device=dev).to(y.feature.dtype)
+            grad_out["n"] = n
+        y.feature.backward(grad_out["g"])
+        flat, plist = sharding.flatten_grads(params)
+        if dist is not None:
+            dist.all_reduce(flat)
+        grad_out["flat"] = flat
+        return y
 
     def step_resident():
-        x = sphconv.SparseConvTensor(d_feat, shape, B, z_idx=d_zidx, z_ptr=d_zptr)
-        return net(x)
+        for f, zi, zp in d_in:
+            y = run_pass(f, zi, zp)
+        return y
 
     out_host = {}
 
     def step_e2e():
-        f = h_feat.to(dev, non_blocking=True)
-        zi = h_zidx.to(dev, non_blocking=True)
-        zp = h_zptr.to(dev, non_blocking=True)
-        y = net(sphconv.SparseConvTensor(f, shape, B, z_idx=zi, z_ptr=zp))
-        for name, t in (("feature", y.feature), ("z_idx", y.z_idx), ("z_ptr", y.z_ptr)):
-            if name not in out_host or out_host[name].shape != t.shape:
-                out_host[name] = torch.empty(t.shape, dtype=t.dtype).pin_memory()
-            out_host[name].copy_(t, non_blocking=True)
+        for c, (hf, hzi, hzp) in enumerate(h_in):
+            y = run_pass(hf.to(dev, non_blocking=True), hzi.to(dev, non_blocking=True), hzp.to(dev, non_blocking=True))
+            outs = (("flat_grad", grad_out["flat"]),) if training else \
+                (("feature", y.feature), ("z_idx", y.z_idx), ("z_ptr", y.z_ptr))
+            for name, t in outs:
+                key = (name, c)
+                if key not in out_host or out_host[key].shape != t.shape:
+                    out_host[key] = torch.empty(t.shape, dtype=t.dtype).pin_memory()
+                out_host[key].copy_(t, non_blocking=True)
         return y
 
     flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)   # > 126 MB L2
@@ -236,7 +278,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    with torch.no_grad():
+    with torch.set_grad_enabled(training):
         sampler = ClockSampler(local_rank) if rank == 0 else None
         t_wall0 = time.time()
         for _ in range(args.warmup):
@@ -257,7 +299,7 @@ def main():
                 tb = rules if not isinstance(rules, torch.Tensor) else rules._sph
                 if id(tb) not in seen_tables:
                     seen_tables[id(tb)] = int((tb.nbr >= 0).sum().item())
-                pairs_of[name] = seen_tables[id(tb)]
+                pairs_of[name] = pairs_of.get(name, 0) + seen_tables[id(tb)]
         profiling.capture_objects = False
         profiling.enable(False)
         del seen_tables, rules, tb, meta
@@ -290,32 +332,34 @@ def main():
         return
 
     peaks = load_peaks()
-    scans = world * B * args.steps
+    scans = world * B * chunks * args.steps
     value = scans / (total_ms * 1e-3)
     e2e_value = scans / (e2e_total_ms * 1e-3)
 
     # ---- per-layer accounting: algorithmic flops = 2*pairs*iC*oC, bytes = e*(rows_in*iC + rows_out*oC) + e*KV*iC*oC + 8*pairs
     layers = {}
     for name, ms, meta in sections:
-        ent = layers.setdefault(name, {"ms": 0.0, "n": 0, "meta": meta})
+        ent = layers.setdefault(name, {"ms": 0.0, "meta": meta})
         ent["ms"] += ms
-        ent["n"] += 1
     layer_rows = []
     tc_flops = tc_ms = 0.0
     conv_ms = rules_ms = 0.0
+    dcode = _capi.DTYPE_CODE[feat_dtype]
     for name, ent in layers.items():
-        ms = ent["ms"] / ent["n"]
+        ms = ent["ms"] / args.steps            # per step (all forward passes of the step together)
         meta = ent["meta"]
-        if name.startswith("conv:"):
-            pairs = pairs_of[name]
+        kind = name.split(":")[0]
+        if kind in ("conv", "dgrad", "wgrad"):
+            pairs = pairs_of.get("conv:" + name.split(":", 1)[1], 0)
             iC, oC, e = meta["iC"], meta["oC"], meta["esize"]
             flops = 2.0 * pairs * iC * oC
-            byts = e * (meta["n_in"] * iC + meta["n_out"] * oC) + e * 27 * iC * oC + 8.0 * pairs
+            byts = chunks * (e * (meta["n_in"] * iC + meta["n_out"] * oC) + e * 27 * iC * oC) + 8.0 * pairs
             tf = flops / (ms * 1e-3) / 1e12
             gbs = byts / (ms * 1e-3) / 1e9
-            uses_tc = bool(lib.sph_conv_uses_tensor_cores(_capi.DTYPE_CODE[dtype], iC, oC))
-            layer_rows.append({"layer": name[5:], "ms": round(ms, 4), "pairs": pairs, "tflops": round(tf, 2),
-                               "gbs": round(gbs, 1), "frac_tensor": round(tf / peaks["tflops"], 4),
+            k_ch, n_ch = (oC, iC) if kind == "dgrad" else (iC, oC)
+            uses_tc = kind != "wgrad" and bool(lib.sph_conv_uses_tensor_cores(dcode, k_ch, n_ch))
+            layer_rows.append({"layer": name if kind != "conv" else name[5:], "ms": round(ms, 4), "pairs": pairs,
+                               "tflops": round(tf, 2), "gbs": round(gbs, 1), "frac_tensor": round(tf / peaks["tflops"], 4),
                                "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "tensor_cores": uses_tc})
             conv_ms += ms
             if uses_tc:
@@ -328,27 +372,31 @@ def main():
     roofline = {"kernel": "conv_gather_tc_kernel (all tensor-core layers of one step)", "bound": "tensor",
                 "achieved": round(achieved, 2), "peak": peaks["tflops"], "unit": "TFLOP/s",
                 "frac": round(achieved / peaks["tflops"], 4), "peak_source": "of " + peaks["source"] + " (burst bf16)",
-                "traffic": TRAFFIC_PER_STEP_BYTES.get((args.workload, B)),
+                "traffic": TRAFFIC_PER_STEP_BYTES.get((args.workload, B * chunks)),
                 "conv_ms_per_step": round(conv_ms, 4), "rules_ms_per_step": round(rules_ms, 4)}
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        dt, _ = cpu_dense_scan(cfg, 0, threads)          # warm-up (thread pool, allocator)
-        dts = [cpu_dense_scan(cfg, 0, threads)[0] for _ in range(2)]
-        cpu = {"value": 1.0 / (sum(dts) / len(dts)), "unit": "scans/s", "cores": threads, "kind": "port",
-               "sample": "1 scan (B=1) of %s through all 8 layers as dense fp32 conv3d on the densified grid, mean of 2" % args.workload}
+        w_div = 4 if args.workload == "cfg5" else 1        # cfg5 scans are 4x wider: time a quarter-azimuth strip
+        dt, _ = cpu_dense_scan(cfg, 0, threads, w_div)    # warm-up (thread pool, allocator)
+        dts = [cpu_dense_scan(cfg, 0, threads, w_div)[0] for _ in range(2)]
+        cpu = {"value": 1.0 / w_div / (sum(dts) / len(dts)), "unit": "scans/s", "cores": threads, "kind": "port",
+               "sample": "%s of one %s scan through all 8 layers (forward) as dense fp32 conv3d on the densified grid, "
+                         "mean of 2" % ("a 1/%d azimuth strip" % w_div if w_div > 1 else "the whole", args.workload)}
 
-    h2d = h_feat.numel() * h_feat.element_size() + h_zidx.numel() * 4 + h_zptr.numel() * 4
+    h2d = sum(t.numel() * t.element_size() for h in h_in for t in h)
     d2h = sum(t.numel() * t.element_size() for t in out_host.values())
     line = {
         "metric": "backbone scans/sec", "value": round(value, 2), "unit": "scans/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 4),
         "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
-        "config": {"workload": "%s: SECOND-style 8-layer encoder, %s inference, grid %s, %d scans per GPU per step"
-                               % (args.workload, dtype_name, "x".join(map(str, shape)), B),
-                   "scans_per_step": world * B, "out_rows_rank0": out_rows, "l2": "256 MB flush write between steps",
-                   "rule_sets_per_step": 5, "conv_layers_per_step": 8},
+        "config": {"workload": "%s: SECOND-style 8-layer encoder, %s %s, grid %s, %d scans per GPU per step"
+                               % (args.workload, dtype_name, "forward+backward+wgrad all-reduce" if training else "inference",
+                                  "x".join(map(str, shape)), B * chunks),
+                   "scans_per_step": world * B * chunks, "scans_per_forward_pass": B, "out_rows_rank0": out_rows,
+                   "l2": "256 MB flush write between steps", "rule_sets_per_step": 5 * chunks,
+                   "conv_layers_per_step": 8 * chunks},
         "e2e": {"value": round(e2e_value, 2), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_total_ms / args.steps, 4)},
         "gpu_launches": int(launches) * args.steps,

@@ -123,6 +123,7 @@ class Conv3d(Convolution):
         bias = self.bias if (self.apply_bias and self.bias is not None) else None
         needs_grad = torch.is_grad_enabled() and (input.feature.requires_grad or self.weight.requires_grad)
         if needs_grad:
+            profiling.current_tag = tag
             out_feature = ConvFunction.apply(input.feature, weight, rules, rule_size, tile_grid_shape,
                                              oz_idx.shape[0])
             if bias is not None:

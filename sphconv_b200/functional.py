@@ -3,8 +3,9 @@ from typing import List
 
 import torch
 
-from .sphconv_cuda import (init_tensor, init_tensor_backward, rule_conv, rule_conv_backward, to_dense,
-                           to_dense_backward)
+from . import profiling
+from .sphconv_cuda import (init_tensor, init_tensor_backward, rule_conv, rule_conv_d_feature, rule_conv_d_weight,
+                           to_dense, to_dense_backward)
 
 
 class ConvFunction(torch.autograd.Function):
@@ -23,7 +24,11 @@ class ConvFunction(torch.autograd.Function):
             ctx.save_for_backward(feature, weight)
             ctx.rule_obj = rules
         ctx.tile_grid_shape = tile_grid_shape
-        return rule_conv(feature, weight, rules, rule_size, outNNZ)
+        ctx.tag = profiling.current_tag
+        with profiling.section("conv:" + ctx.tag, iC=weight.shape[1], oC=weight.shape[2], n_in=feature.shape[0],
+                               n_out=int(outNNZ), esize=feature.element_size(),
+                               rules=rules if profiling.capture_objects else None):
+            return rule_conv(feature, weight, rules, rule_size, outNNZ)
 
     @staticmethod
     def backward(ctx, d_featureOut: torch.Tensor):
@@ -32,10 +37,16 @@ class ConvFunction(torch.autograd.Function):
         else:
             feature, weight = ctx.saved_tensors
             rules, rule_size = ctx.rule_obj, None
-        # the op takes the [KV,oC,iC] transpose, as in the reference (sphconv/functional.py:70-74)
-        d_feature, d_weight = rule_conv_backward(
-            d_featureOut.contiguous(), feature, weight.permute(0, 2, 1).contiguous(), rules, rule_size,
-            ctx.tile_grid_shape)
+        # the ops take the [KV,oC,iC] transpose, as in the reference (sphconv/functional.py:70-74); this is
+        # rule_conv_backward (src/sphconv/rule_conv.cu:577-597) spelled out so the two halves can be timed
+        d_out = d_featureOut.contiguous()
+        meta = dict(iC=weight.shape[1], oC=weight.shape[2], n_in=feature.shape[0], n_out=d_out.shape[0],
+                    esize=feature.element_size())
+        with profiling.section("dgrad:" + ctx.tag, **meta):
+            d_feature = rule_conv_d_feature(d_out, weight.permute(0, 2, 1).contiguous(), rules, rule_size,
+                                            ctx.tile_grid_shape, feature.shape[0])
+        with profiling.section("wgrad:" + ctx.tag, **meta):
+            d_weight = rule_conv_d_weight(feature, d_out, rules, rule_size).to(feature.dtype)
         return d_feature, d_weight, None, None, None, None
 
 

@@ -5,6 +5,7 @@ import torch
 
 _active = False
 capture_objects = False   # sections may attach tensors to their meta only while this is set (they stay alive until collect)
+current_tag = ""          # name of the layer whose ops are being issued (set by Conv3d.forward)
 _records = []   # (name, start_event, stop_event, meta)
 
 
