@@ -171,6 +171,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
+    torch.cuda.set_per_process_memory_fraction(0.8, local_rank)   # stay well inside the device: a dead box helps nobody
     dev = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
@@ -288,21 +289,11 @@ def main():
         out_rows = int(y.feature.shape[0])
 
         # pairs per layer (for the algorithmic flop / byte counts), from one untimed step
-        profiling.enable(True)
-        profiling.capture_objects = True
+        profiling.pair_counts = {}
         step_resident()
-        pairs_of = {}
-        seen_tables = {}
-        for name, _, meta in profiling.collect():
-            if name.startswith("conv:"):
-                rules = meta["rules"]
-                tb = rules if not isinstance(rules, torch.Tensor) else rules._sph
-                if id(tb) not in seen_tables:
-                    seen_tables[id(tb)] = int((tb.nbr >= 0).sum().item())
-                pairs_of[name] = pairs_of.get(name, 0) + seen_tables[id(tb)]
-        profiling.capture_objects = False
-        profiling.enable(False)
-        del seen_tables, rules, tb, meta
+        torch.cuda.synchronize()
+        pairs_of = dict(profiling.pair_counts)
+        profiling.pair_counts = None
 
         # ---- resident-input timing (value), with per-layer sections for the roofline
         barrier()

@@ -133,8 +133,8 @@ class Conv3d(Convolution):
         else:
             weight = self._cached_packed(weight)
             with profiling.section("conv:" + tag, iC=in_channels, oC=out_channels, n_in=input.feature.shape[0],
-                                   n_out=oz_idx.shape[0], esize=input.feature.element_size(),
-                                   rules=rules if profiling.capture_objects else None):
+                                   n_out=oz_idx.shape[0], esize=input.feature.element_size()):
+                profiling.count_pairs("conv:" + tag, rules)
                 out_feature = ops.rule_conv(input.feature, weight, rules, rule_size, oz_idx.shape[0],
                                             bias=None if bias is None else bias.detach().float(),
                                             relu=self.activation == 'relu')

@@ -26,8 +26,8 @@ class ConvFunction(torch.autograd.Function):
         ctx.tile_grid_shape = tile_grid_shape
         ctx.tag = profiling.current_tag
         with profiling.section("conv:" + ctx.tag, iC=weight.shape[1], oC=weight.shape[2], n_in=feature.shape[0],
-                               n_out=int(outNNZ), esize=feature.element_size(),
-                               rules=rules if profiling.capture_objects else None):
+                               n_out=int(outNNZ), esize=feature.element_size()):
+            profiling.count_pairs("conv:" + ctx.tag, rules)
             return rule_conv(feature, weight, rules, rule_size, outNNZ)
 
     @staticmethod

@@ -4,7 +4,7 @@ import contextlib
 import torch
 
 _active = False
-capture_objects = False   # sections may attach tensors to their meta only while this is set (they stay alive until collect)
+pair_counts = None        # dict name -> pairs: while set, count_pairs() accumulates into it (synchronising)
 current_tag = ""          # name of the layer whose ops are being issued (set by Conv3d.forward)
 _records = []   # (name, start_event, stop_event, meta)
 
@@ -43,3 +43,15 @@ def collect(reset=True):
     if reset:
         _records.clear()
     return out
+
+
+def count_pairs(name, rules):
+    """When pair counting is switched on, add the number of (in,out) pairs of this rule set to pair_counts[name].
+    Counts at once and keeps no reference to the (possibly GB-sized) rule tensors."""
+    if pair_counts is None:
+        return
+    tb = rules if not isinstance(rules, torch.Tensor) else getattr(rules, "_sph", None)
+    if tb is None:
+        return
+    n = int((tb.nbr >= 0).sum().item())
+    pair_counts[name] = pair_counts.get(name, 0) + n

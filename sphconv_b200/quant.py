@@ -48,7 +48,8 @@ class QuantConv:
                 x.rule_cache[c.indice_key] = datas
         oz_idx, oz_ptr, rules, rule_size, _ = datas
         with profiling.section("conv:" + tag, iC=c.in_channels, oC=c.out_channels, n_in=x.feature.shape[0],
-                               n_out=oz_idx.shape[0], esize=1, rules=rules if profiling.capture_objects else None):
+                               n_out=oz_idx.shape[0], esize=1):
+            profiling.count_pairs("conv:" + tag, rules)
             y = ops.rule_conv(x.feature, self.weight_q, rules, rule_size, oz_idx.shape[0], scale=self.scale,
                               bias=self.bias, relu=self.relu, out_dtype=self.out_dtype)
         out = SparseConvTensor(y, out_shape, x.B, z_ptr=oz_ptr, z_idx=oz_idx)

@@ -50,19 +50,24 @@ def test_encoder_inference_vs_dense(dtype):
     assert sphconv.check_status() == 0
 
 
-def test_encoder_training_step_bf16_vs_dense_autograd():
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-3), (torch.bfloat16, 1e-1)])
+def test_encoder_training_step_vs_dense_autograd(dtype, tol):
+    """Forward + backward of all eight layers against autograd through the dense fp32 stack on the same
+    (rounded) parameters.  fp32 must agree tightly.  For bf16 the per-layer 1e-2 bound is checked in
+    test_gpu_conv.py; across eight layers a rounded activation near zero can flip a ReLU and reroute a gradient
+    path, so the end-to-end bound is looser."""
     b = _batch(1)
-    net = build_encoder8(dtype=torch.bfloat16, device=DEV).train()
-    x = _tensor(b, torch.bfloat16, requires_grad=True)
+    net = build_encoder8(dtype=dtype, device=DEV).train()
+    x = _tensor(b, dtype, requires_grad=True)
     y = net(x)
-    g = torch.as_tensor(np.random.default_rng(1).standard_normal(tuple(y.feature.shape)), device=DEV).to(torch.bfloat16)
+    g = torch.as_tensor(np.random.default_rng(1).standard_normal(tuple(y.feature.shape)), device=DEV).to(dtype)
     y.feature.backward(g)
-    # dense fp32 autograd of the same stack on the same rounded parameters
     ws = [m.weight.detach().float().cpu().requires_grad_(True) for m in net._modules.values()]
     bs = [m.bias.detach().float().cpu().requires_grad_(True) for m in net._modules.values()]
-    feat = torch.as_tensor(b["feature"]).to(torch.bfloat16).float().requires_grad_(True)
+    feat = torch.as_tensor(b["feature"]).to(dtype).float().requires_grad_(True)
     B, shape = b["B"], b["shape"]
-    bb, xx, yy, zz = [torch.as_tensor(a) for a in __import__("oracle.rules_np", fromlist=["x"]).row_coords(b["z_idx"], b["z_ptr"], B, *shape[:2])]
+    from oracle.rules_np import row_coords
+    bb, xx, yy, zz = [torch.as_tensor(a) for a in row_coords(b["z_idx"], b["z_ptr"], B, *shape[:2])]
     d = torch.zeros((B, shape[0], shape[1], shape[2], 4)).index_put((bb, xx, yy, zz), feat).permute(0, 4, 1, 2, 3)
     mask = torch.zeros((B, 1, *shape)).index_put((bb, torch.zeros_like(bb), xx, yy, zz), torch.ones(bb.shape[0])) != 0
     for (subm, iC, oC, stride, key), w, bias in zip(synthetic.ENCODER8, ws, bs):
@@ -73,12 +78,12 @@ def test_encoder_training_step_bf16_vs_dense_autograd():
             d = torch.nn.functional.conv3d(d, wd, None, stride, 1)
             mask = torch.nn.functional.conv3d(mask.float(), torch.ones((1, 1, 3, 3, 3)), None, stride, 1) != 0
         d = torch.relu(d + bias.view(1, -1, 1, 1, 1)) * mask
-    # upstream gradient placed at the output sites
     gd = sphconv.SparseConvTensor(g.float(), [y.D, y.W, y.H], B, z_idx=y.z_idx, z_ptr=y.z_ptr).dense().cpu()
     d.backward(gd)
-    assert _rel_l2(x.feature.grad.float().cpu(), feat.grad) <= 5e-2      # eight bf16 layers of forward + backward
-    for m, w in zip(net._modules.values(), ws):
-        assert _rel_l2(m.weight.grad.float().cpu(), w.grad) <= 5e-2
+    errs = {"y": _rel_l2(y.dense().float().cpu(), d.detach()), "dx": _rel_l2(x.feature.grad.float().cpu(), feat.grad)}
+    for li, (m, w) in enumerate(zip(net._modules.values(), ws)):
+        errs["dw%d" % li] = _rel_l2(m.weight.grad.float().cpu(), w.grad)
+    assert max(errs.values()) <= tol, errs
     assert sphconv.check_status() == 0
 
 
