@@ -347,7 +347,7 @@ def main():
             byts = chunks * (e * (meta["n_in"] * iC + meta["n_out"] * oC) + e * 27 * iC * oC) + 8.0 * pairs
             tf = flops / (ms * 1e-3) / 1e12
             gbs = byts / (ms * 1e-3) / 1e9
-            k_ch, n_ch = (oC, iC) if kind == "dgrad" else (iC, oC)
+            k_ch, n_ch = (oC, iC) if kind == "dgrad" else (meta.get("k_ch", iC), meta.get("n_ch", oC))
             uses_tc = kind != "wgrad" and bool(lib.sph_conv_uses_tensor_cores(dcode, k_ch, n_ch))
             layer_rows.append({"layer": name if kind != "conv" else name[5:], "ms": round(ms, 4), "pairs": pairs,
                                "tflops": round(tf, 2), "gbs": round(gbs, 1), "frac_tensor": round(tf / peaks["tflops"], 4),

@@ -48,7 +48,7 @@ class QuantConv:
                 x.rule_cache[c.indice_key] = datas
         oz_idx, oz_ptr, rules, rule_size, _ = datas
         with profiling.section("conv:" + tag, iC=c.in_channels, oC=c.out_channels, n_in=x.feature.shape[0],
-                               n_out=oz_idx.shape[0], esize=1):
+                               n_out=oz_idx.shape[0], esize=1, k_ch=self.weight_q.shape[1], n_ch=self.weight_q.shape[2]):
             profiling.count_pairs("conv:" + tag, rules)
             y = ops.rule_conv(x.feature, self.weight_q, rules, rule_size, oz_idx.shape[0], scale=self.scale,
                               bias=self.bias, relu=self.relu, out_dtype=self.out_dtype)
@@ -60,12 +60,15 @@ class QuantConv:
 class QuantEncoder:
     """Chain of QuantConv layers; `quantize_input` turns float features into the first layer's int8 input."""
 
-    def __init__(self, layers: List[QuantConv], in_scale: torch.Tensor):
-        self.layers, self.in_scale = layers, in_scale
+    def __init__(self, layers: List[QuantConv], in_scale: torch.Tensor, in_channels_padded: int):
+        self.layers, self.in_scale, self.in_channels_padded = layers, in_scale, in_channels_padded
 
     def quantize_input(self, feature: torch.Tensor) -> torch.Tensor:
-        q = torch.round(feature.float() / self.in_scale).clamp_(-QMAX, QMAX)
-        return q.to(torch.int8)
+        """float [n, C] -> int8 [n, C padded to 32] (zeros in the padding)."""
+        q = torch.round(feature.float() / self.in_scale).clamp_(-QMAX, QMAX).to(torch.int8)
+        out = torch.zeros((q.shape[0], self.in_channels_padded), dtype=torch.int8, device=q.device)
+        out[:, :q.shape[1]] = q
+        return out
 
     def __call__(self, x: SparseConvTensor) -> SparseConvTensor:
         for layer in self.layers:
@@ -85,15 +88,26 @@ def quantize_encoder(net: Sequential, calib: SparseConvTensor) -> QuantEncoder:
     for m in convs:
         acts.append(_absmax_per_channel(x.feature))
         x = m(x)
+    # int8 rows must be at least 32 bytes for the tensor-core kernel (one kind::i8 instruction consumes 32 channels),
+    # so channel counts are padded to a multiple of 32 with zero weights: a padded output channel computes
+    # relu(0) = 0 and the next layer's padded input channels carry zero weights.
+    pad = lambda c: max(32, (c + 31) // 32 * 32)
     layers = []
     for li, m in enumerate(convs):
-        s_x = acts[li] / QMAX                                         # [iC]
-        w = m.weight.detach().float().reshape(-1, m.in_channels, m.out_channels) * s_x.view(1, -1, 1)
-        s_w = w.abs().amax(dim=(0, 1)).clamp_min(1e-12) / QMAX       # [oC]
-        w_q = torch.round(w / s_w.view(1, 1, -1)).clamp_(-QMAX, QMAX).to(torch.int8).contiguous()
-        bias = m.bias.detach().float() if (m.apply_bias and m.bias is not None) else torch.zeros_like(s_w)
         last = li == len(convs) - 1
+        iC, oC = m.in_channels, m.out_channels
+        iP, oP = pad(iC), (oC if last else pad(oC))
+        s_x = acts[li] / QMAX                                         # [iC]
+        w = m.weight.detach().float().reshape(-1, iC, oC) * s_x.view(1, -1, 1)
+        s_w = w.abs().amax(dim=(0, 1)).clamp_min(1e-12) / QMAX       # [oC]
+        w_q = torch.zeros((w.shape[0], iP, oP), dtype=torch.int8, device=w.device)
+        w_q[:, :iC, :oC] = torch.round(w / s_w.view(1, 1, -1)).clamp_(-QMAX, QMAX).to(torch.int8)
+        bias = m.bias.detach().float() if (m.apply_bias and m.bias is not None) else torch.zeros_like(s_w)
         s_y = torch.ones_like(s_w) if last else acts[li + 1] / QMAX
-        layers.append(QuantConv(m, w_q, (s_w / s_y).contiguous(), (bias / s_y).contiguous(), m.activation == 'relu',
+        scale = torch.ones(oP, device=w.device)
+        bias_p = torch.zeros(oP, device=w.device)
+        scale[:oC] = s_w / s_y
+        bias_p[:oC] = bias / s_y
+        layers.append(QuantConv(m, w_q.contiguous(), scale.contiguous(), bias_p.contiguous(), m.activation == 'relu',
                                 torch.float32 if last else torch.int8))
-    return QuantEncoder(layers, acts[0] / QMAX)
+    return QuantEncoder(layers, acts[0] / QMAX, pad(convs[0].in_channels))
