@@ -359,11 +359,19 @@ def main():
         else:
             rules_ms += ms
             layer_rows.append({"layer": name, "ms": round(ms, 4)})
-    achieved = tc_flops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
-    roofline = {"kernel": "conv_gather_tc_kernel (all tensor-core layers of one step)", "bound": "tensor",
+    all_tc = tc_flops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
+    # dominant kernel: the tensor-core convolution of the widest layers (L6 / L7: 64 -> 64), one launch per layer and pass
+    dom = [r for r in layer_rows if r.get("layer") in ("L6", "L7")]
+    dom_ms = sum(r["ms"] for r in dom) / max(1, len(dom) * chunks)            # average launch duration
+    dom_flops = sum(2.0 * r["pairs"] * 64 * 64 for r in dom) / max(1, len(dom) * chunks)
+    achieved = dom_flops / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
+    traffic = TRAFFIC_BYTES_PER_OUT_ROW.get(dtype_name)
+    roofline = {"kernel": "conv_gather_tc_kernel<8> on the 64->64 layers (L6, L7), per launch", "bound": "tensor",
                 "achieved": round(achieved, 2), "peak": peaks["tflops"], "unit": "TFLOP/s",
                 "frac": round(achieved / peaks["tflops"], 4), "peak_source": "of " + peaks["source"] + " (burst bf16)",
-                "traffic": TRAFFIC_PER_STEP_BYTES.get((args.workload, B * chunks)),
+                "launch_ms": round(dom_ms, 4), "flops_per_launch": dom_flops,
+                "traffic": None if traffic is None else int(traffic * out_rows),
+                "all_tensor_core_layers_tflops": round(all_tc, 2),
                 "conv_ms_per_step": round(conv_ms, 4), "rules_ms_per_step": round(rules_ms, 4)}
 
     cpu = None
@@ -402,9 +410,9 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of the tensor-core convolution launches of one step, from the ncu capture
-# summarised under profiles/; keyed by (workload, scans per GPU).  None until captured for that case.
-TRAFFIC_PER_STEP_BYTES = {}
+# DRAM bytes (read + write) per output row of one launch of the dominant kernel, from the ncu capture summarised in
+# profiles/conv_gather_tc_64to64_fp16_b4_full.md (97.8 MB for 346.8 k rows); traffic grows in proportion to rows.
+TRAFFIC_BYTES_PER_OUT_ROW = {"fp16": 282.0}
 
 if __name__ == "__main__":
     main()
