@@ -33,6 +33,10 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
 bool conv_tc_supported(int dtype, int kv, int K, int N);
 int64_t packed_weight_bytes(int dtype, int kv, int K, int N);
 int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cudaStream_t st);
+// conv_wgrad_tc.cu
+bool conv_wgrad_tc_supported(int dtype, int kv, int K, int N);
+int conv_wgrad_tc(const void* rows, const void* dout, int dtype, int64_t n_rows, const int* nbr, int64_t n_out, int kv,
+                  int K, int N, float* dw, int* status, cudaStream_t st);
 
 }  // namespace sph
 
@@ -93,5 +97,7 @@ extern "C" int sph_conv_wgrad(const void* d_rows, const void* d_dout, int dtype,
   if (zero_init) SPH_CUDA(cudaMemsetAsync(d_dweight, 0, (size_t)kv * k_ch * n_ch * sizeof(float), st));
   if (n_out == 0 || n_rows == 0) return SPH_OK;
   SPH_CHECK_ARG(d_rows && d_dout && d_nbr, "null pointer");
+  if (conv_wgrad_tc_supported(dtype, kv, k_ch, n_ch))
+    return conv_wgrad_tc(d_rows, d_dout, dtype, n_rows, d_nbr, n_out, kv, k_ch, n_ch, d_dweight, d_status, st);
   return conv_wgrad_generic(d_rows, d_dout, dtype, n_rows, d_nbr, n_out, kv, k_ch, n_ch, d_dweight, d_status, st);
 }

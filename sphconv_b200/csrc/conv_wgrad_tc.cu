@@ -1,0 +1,293 @@
+// Weight gradient on the tensor cores (fp16 / bf16):  dW[k] (iC x oC) = sum_r X[nbr[k][r], :]^T  dY[r, :].
+//
+// The sum over output rows is the MMA's K dimension.  Both operands are "MN-major" views of row tiles that sit
+// in shared memory in the same 8-row x 16-byte core-matrix layout the forward kernel gathers into:
+//   A = X_k^T  : M = iC (padded to 64 with zero chunk planes, or 128), K = 256 gathered rows of offset k
+//   B = dY     : N = oC, K = the same 256 output rows (a plain contiguous copy, not a gather)
+//   D = dW[k]  : fp32 in TMEM, one accumulator per kernel offset.
+// TMEM holds 512 columns, i.e. floor(512/oC) accumulators, so the 27 offsets are split into groups and the grid
+// into (row-tile slice) x (offset group): a CTA keeps its group's accumulators in TMEM across ALL of its tiles and
+// adds them to the fp32 gradient once at the end with red.global.add.f32 (the reference writes a partial per
+// tile, [NTile,KV,iC,oC], and torch::sum's them, src/sphconv/rule_conv.cu:483-484,517).
+//
+// Warps 0-7 copy (dY tile once per tile, X_k tile once per offset), warp 8 issues the MMAs; the final flush is
+// done by warps 0-3.  Same bounded waits and abort path as the forward kernel.
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace sph {
+
+namespace {
+
+using namespace tc;
+
+constexpr int kTileRows = 256;
+constexpr int kCopyWarps = 8;
+constexpr int kCopyThreads = kCopyWarps * 32;
+constexpr int kMmaWarp = kCopyWarps;
+constexpr int kThreads = (kCopyWarps + 1) * 32;
+constexpr int kRowsPerWarp = kTileRows / kCopyWarps;
+constexpr uint32_t kPlane = kTileRows * 16 + 16;   // bytes of one chunk plane (256 rows x 16 B + bank skew)
+constexpr int kMaxStages = 6;
+constexpr int kSmemTotal = 227 * 1024 - 4096;   // dynamic shared memory next to the 3 KB static part
+
+struct WgParams {
+  const void* rows;     // X [n_rows, K]
+  const void* dout;     // dY [n_out, N]
+  const int* nbr;       // [KV][n_out]
+  float* dw;            // [KV][K][N] fp32, accumulated into
+  int64_t n_rows, n_out;
+  int kv, K, N;
+  int kc_x, kc_y;       // 16-byte chunks per X row / dY row
+  int planes_x;         // chunk planes of an X tile (>= kc_x; the extra ones are zero and pad M to 64)
+  int MP;               // UMMA M: 64 or 128
+  int is_bf16;
+  int groups;           // offset groups
+  int per_group;        // offsets per group
+  int slices;           // row-tile slices = gridDim.x / groups
+  int num_tiles;
+  int stages;
+  int x_bytes, y_bytes; // bytes of one X tile / one dY tile in shared memory
+  int y_off, x_off;     // dynamic shared memory offsets
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ __align__(8) uint64_t s_full[kMaxStages];
+  __shared__ __align__(8) uint64_t s_empty[kMaxStages];
+  __shared__ __align__(8) uint64_t s_yfull[2];
+  __shared__ __align__(8) uint64_t s_yempty[2];
+  __shared__ __align__(8) uint64_t s_done;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int S = p.stages;
+  const int grp = (int)blockIdx.x % p.groups;       // which offsets
+  const int slice = (int)blockIdx.x / p.groups;     // which tiles: slice, slice + slices, ...
+  const int k_begin = grp * p.per_group;
+  const int k_end = min(p.kv, k_begin + p.per_group);
+  const int nk = k_end - k_begin;
+  const int my_tiles = slice < p.num_tiles ? (p.num_tiles - slice + p.slices - 1) / p.slices : 0;
+  uint8_t* y_smem = smem + p.y_off;
+  uint8_t* x_smem = smem + p.x_off;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&s_full[s]), kCopyThreads);
+      mbar_init(smem_u32(&s_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&s_yfull[b]), kCopyThreads);
+      mbar_init(smem_u32(&s_yempty[b]), 1);
+    }
+    mbar_init(smem_u32(&s_done), 1);
+    mbar_init_fence();
+  }
+  // zero the padding planes of every X stage once: the gathers never touch them
+  if (p.planes_x > p.kc_x) {
+    for (int s = 0; s < S; ++s) {
+      uint4* z = (uint4*)(x_smem + (size_t)s * p.x_bytes + (size_t)p.kc_x * kPlane);
+      const int n16 = (p.planes_x - p.kc_x) * (int)kPlane / 16;
+      for (int i = tid; i < n16; i += kThreads) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async();   // generic-proxy stores that the tensor core will read
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&s_tmem_base), 512u);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp < kCopyWarps) {
+    // ======================= copy warps =======================
+    // lpr lanes copy the chunks of one row; a lane serves `lpr` consecutive rows of its warp's 32
+    auto copy_rows = [&](uint32_t dst_tile, const uint8_t* base, int kc, uint32_t row_bytes, const int* ids,
+                         unsigned limit) {
+      const int lpr = kc < 8 ? kc : 8;
+      const int passes = kc / lpr;
+      const int l_chunk = lane % lpr;
+      const int l_row0 = (lane / lpr) * lpr;
+      const uint32_t dst0 = dst_tile + (uint32_t)l_chunk * kPlane + (uint32_t)(warp * kRowsPerWarp + l_row0) * 16u;
+      for (int j = 0; j < lpr; ++j) {
+        const int id = ids[l_row0 + j];
+        const bool present = (unsigned)id < limit;
+        const uint8_t* src = base + (size_t)(present ? (uint32_t)id : 0u) * row_bytes + l_chunk * 16;
+        const uint32_t sz = present ? 16u : 0u;
+        for (int q = 0; q < passes; ++q) cp_async_16(dst0 + (uint32_t)j * 16u + (uint32_t)q * 8u * kPlane, src + q * 128, sz);
+      }
+    };
+    __shared__ int s_ids[kCopyWarps][2][kRowsPerWarp];   // per warp: [0] output-row ids, [1] neighbour ids of one offset
+    int s = 0;
+    uint32_t par = 1u;
+    bool dead = false;
+    for (int ti = 0; ti < my_tiles && !dead; ++ti) {
+      const int tile = slice + ti * p.slices;
+      const int64_t r = (int64_t)tile * kTileRows + warp * kRowsPerWarp + lane;
+      const int yb = ti & 1;
+      // ---- dY tile (contiguous rows)
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(smem_u32(&s_yempty[yb]), (((uint32_t)ti >> 1) & 1u) ^ 1u, abort_flag);
+      if (__any_sync(0xffffffffu, !ok)) { dead = true; break; }
+      s_ids[warp][0][lane] = r < p.n_out ? (int)r : -1;
+      __syncwarp();
+      copy_rows(smem_u32(y_smem + (size_t)yb * p.y_bytes), (const uint8_t*)p.dout, p.kc_y, (uint32_t)p.kc_y * 16u,
+                s_ids[warp][0], (unsigned)p.n_out);
+      cp_async_arrive_noinc(smem_u32(&s_yfull[yb]));
+      // ---- one gathered X tile per offset of this CTA's group
+      for (int k = k_begin; k < k_end; ++k) {
+        const int nb = r < p.n_out ? __ldg(p.nbr + (int64_t)k * p.n_out + r) : -1;
+        if (lane == 0) ok = mbar_wait(smem_u32(&s_empty[s]), par, abort_flag);
+        if (__any_sync(0xffffffffu, !ok)) { dead = true; break; }
+        s_ids[warp][1][lane] = nb;
+        __syncwarp();
+        copy_rows(smem_u32(x_smem + (size_t)s * p.x_bytes), (const uint8_t*)p.rows, p.kc_x, (uint32_t)p.kc_x * 16u,
+                  s_ids[warp][1], (unsigned)p.n_rows);
+        cp_async_arrive_noinc(smem_u32(&s_full[s]));
+        __syncwarp();
+        if (++s == S) { s = 0; par ^= 1u; }
+      }
+    }
+    cp_async_wait_all();
+  } else if (lane == 0) {
+    // ======================= MMA issuer =======================
+    // both operands MN-major: SBO = stride between 8-element blocks along M/N (= chunk planes),
+    // LBO = stride between 8-row groups along K (= 128 bytes); one instruction consumes 16 rows = 2 groups
+    const uint32_t idesc = make_idesc(1u, p.is_bf16 ? 1u : 0u, 1u, 1u, (uint32_t)p.MP, (uint32_t)p.N);
+    const uint64_t d0 = make_smem_desc(0u, 128u, kPlane);
+    const uint64_t hi = d0 & 0xffffffff00000000ull;
+    const uint32_t lo0 = (uint32_t)d0;
+    int s = 0;
+    uint32_t par = 0u;
+    bool dead = false;
+    for (int ti = 0; ti < my_tiles && !dead; ++ti) {
+      const int yb = ti & 1;
+      if (!mbar_wait(smem_u32(&s_yfull[yb]), ((uint32_t)ti >> 1) & 1u, abort_flag)) break;
+      const uint32_t y_lo = lo0 + (smem_u32(y_smem + (size_t)yb * p.y_bytes) >> 4);
+      for (int k = 0; k < nk; ++k) {
+        if (!mbar_wait(smem_u32(&s_full[s]), par, abort_flag)) { dead = true; break; }
+        fence_proxy_async();
+        tc_fence_after();
+        const uint32_t x_lo = lo0 + (smem_u32(x_smem + (size_t)s * p.x_bytes) >> 4);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(k * p.N);
+#pragma unroll 4
+        for (int j = 0; j < kTileRows / 16; ++j) {
+          const uint32_t step = (uint32_t)j * ((2u * 128u) >> 4);
+          umma_f16(d_tmem, hi | (uint64_t)(x_lo + step), hi | (uint64_t)(y_lo + step), idesc, (ti | j) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&s_empty[s]));
+        if (++s == S) { s = 0; par ^= 1u; }
+      }
+      if (!dead) umma_commit(smem_u32(&s_yempty[yb]));
+    }
+    umma_commit(smem_u32(&s_done));
+    mbar_wait(smem_u32(&s_done), 0u, abort_flag);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // ======================= flush: warps 0-3 add the accumulators to the fp32 gradient =======================
+  if (!s_abort && warp < 4 && my_tiles > 0) {
+    const int q = warp;
+    const int ic = p.MP == 64 ? (lane < 16 ? 16 * q + lane : -1) : 32 * q + lane;
+    for (int k = 0; k < nk; ++k) {
+      for (int c0 = 0; c0 < p.N; c0 += 16) {
+        uint32_t raw[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(k * p.N + c0), raw);
+        tmem_ld_wait();
+        if (ic >= 0 && ic < p.K) {
+          float* dst = p.dw + ((int64_t)(k_begin + k) * p.K + ic) * p.N + c0;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < p.N) atomicAdd(dst + j, __uint_as_float(raw[j]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (s_abort) {
+    if (warp < kCopyWarps) cp_async_wait_all();
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000ll) { }
+    if (tid == 0 && p.status) atomicOr(p.status, SPH_STATUS_TIMEOUT);
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512u);
+  }
+}
+
+bool wgrad_plan(WgParams* p, int dtype, int kv, int K, int N) {
+  if (dtype != SPH_F16 && dtype != SPH_BF16) return false;
+  const int xb = K * 2, yb = N * 2;
+  if (xb != 32 && xb != 64 && xb != 128 && xb != 256) return false;   // same row widths as the forward kernel
+  if (yb != 32 && yb != 64 && yb != 128 && yb != 256) return false;
+  if (kv < 1 || kv > 64) return false;
+  p->kv = kv; p->K = K; p->N = N;
+  p->kc_x = xb / 16; p->kc_y = yb / 16;
+  p->MP = K <= 64 ? 64 : 128;
+  if (p->MP == 128 && N % 16 != 0) return false;
+  p->planes_x = p->MP / 8;
+  p->x_bytes = p->planes_x * (int)kPlane;
+  p->y_bytes = p->kc_y * (int)kPlane;
+  const int acc_max = 512 / N;                      // accumulators that fit in TMEM
+  p->groups = (kv + acc_max - 1) / acc_max;
+  p->per_group = (kv + p->groups - 1) / p->groups;
+  p->y_off = 0;
+  p->x_off = 2 * p->y_bytes;
+  int stages = (kSmemTotal - p->x_off) / p->x_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return false;
+  p->stages = stages;
+  return true;
+}
+
+}  // namespace
+
+bool conv_wgrad_tc_supported(int dtype, int kv, int K, int N) {
+  WgParams p;
+  return wgrad_plan(&p, dtype, kv, K, N);
+}
+
+int conv_wgrad_tc(const void* rows, const void* dout, int dtype, int64_t n_rows, const int* nbr, int64_t n_out, int kv,
+                  int K, int N, float* dw, int* status, cudaStream_t st) {
+  WgParams p;
+  if (!wgrad_plan(&p, dtype, kv, K, N)) {
+    set_error("conv_wgrad_tc: unsupported dtype/shape");
+    return SPH_ERR_UNSUPPORTED;
+  }
+  p.rows = rows; p.dout = dout; p.nbr = nbr; p.dw = dw;
+  p.n_rows = n_rows; p.n_out = n_out;
+  p.is_bf16 = dtype == SPH_BF16;
+  p.status = status;
+  p.num_tiles = (int)div_up64(n_out, kTileRows);
+  static int s_sms = 0;
+  if (s_sms == 0) {
+    int dev = 0;
+    SPH_CUDA(cudaGetDevice(&dev));
+    SPH_CUDA(cudaDeviceGetAttribute(&s_sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  int slices = s_sms / p.groups;
+  if (slices > p.num_tiles) slices = p.num_tiles;
+  if (slices < 1) slices = 1;
+  p.slices = slices;
+  const int grid = slices * p.groups;
+  const int smem_bytes = p.x_off + p.stages * p.x_bytes;
+  SPH_CUDA(cudaFuncSetAttribute(conv_wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  conv_wgrad_tc_kernel<<<grid, kThreads, smem_bytes, st>>>(p);
+  SPH_LAUNCH_CHECK();
+  return SPH_OK;
+}
+
+}  // namespace sph
