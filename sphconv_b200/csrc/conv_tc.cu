@@ -24,7 +24,8 @@
 //
 // Shared-memory operand layout (no swizzle): 8-row x 16-byte core matrices of 128 contiguous bytes;
 // rows: core (row group g, chunk c) at c*4112 + g*128; weights: core (channel group gn, chunk c) at
-// c*(MP/8)*128 + gn*128.
+// c*(N/8)*128 + gn*128 (images hold the N real channels only: the rows up to M = 64/128 that the instruction also
+// reads are whatever follows in shared memory and only feed accumulator rows nobody reads).
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -53,7 +54,7 @@ constexpr uint32_t kRowsLbo = kTileRows * 16 + 16;
 
 struct TcParams {
   const void* rows;
-  const void* packed;   // [KV] images of W[k]^T, each MP x K_ch, K-major
+  const void* packed;   // [KV] images of W[k]^T, each N x K_ch, K-major
   const int* nbr;       // [KV][n_out]
   int64_t n_rows, n_out;
   int kv, K, N;         // channels gathered / produced
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
                                 : make_idesc(1u, p.is_bf16 ? 1u : 0u, 0u, 0u, (uint32_t)p.MP, kTileRows);
       // Descriptors are a constant high word plus a low word that only needs adds (start address and LBO
       // live in the low 32 bits, in 16-byte units).
-      const uint32_t lbo_w = (uint32_t)(p.MP / 8) * 128u;
+      const uint32_t lbo_w = (uint32_t)(p.N / 8) * 128u;
       const uint64_t w_desc0 = make_smem_desc(0u, lbo_w, 128u);
       const uint64_t x_desc0 = make_smem_desc(0u, kRowsLbo, 128u);
       const uint64_t w_hi = w_desc0 & 0xffffffff00000000ull, x_hi = x_desc0 & 0xffffffff00000000ull;
@@ -390,10 +391,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   }
 }
 
-// [KV][K][N] row-major weights -> per-offset UMMA image of W[k]^T ([MP x K], K-major, no swizzle);
-// rows N..MP-1 of every image stay zero (the buffer is cleared first).
+// [KV][K][N] row-major weights -> per-offset UMMA image of W[k]^T ([N x K], K-major, no swizzle).
 template <typename T>
-__global__ void pack_weight_kernel(const T* __restrict__ w, int kv, int K, int N, int MP, T* __restrict__ packed) {
+__global__ void pack_weight_kernel(const T* __restrict__ w, int kv, int K, int N, T* __restrict__ packed) {
   const int64_t total = (int64_t)kv * K * N;
   const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= total) return;
@@ -401,8 +401,8 @@ __global__ void pack_weight_kernel(const T* __restrict__ w, int kv, int K, int N
   const int ic = (int)((e / N) % K);
   const int k = (int)(e / ((int64_t)N * K));
   const int cpe = 16 / (int)sizeof(T);  // elements per 16-byte chunk
-  const int64_t img = (int64_t)k * K * MP;
-  const int64_t off_bytes = (int64_t)(ic / cpe) * (MP / 8) * 128 + (oc / 8) * 128 + (oc % 8) * 16 + (ic % cpe) * (int)sizeof(T);
+  const int64_t img = (int64_t)k * K * N;
+  const int64_t off_bytes = (int64_t)(ic / cpe) * (N / 8) * 128 + (oc / 8) * 128 + (oc % 8) * 16 + (ic % cpe) * (int)sizeof(T);
   packed[img + off_bytes / (int64_t)sizeof(T)] = w[e];
 }
 
@@ -418,17 +418,23 @@ bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   p->w_off = off;
   const int gk = p->kc == 2 ? 4 : p->kc == 4 ? 2 : 1;   // kernel offsets per stage (must match the kernel's GK)
   const int w_all = kv * p->w_bytes;
-  p->w_resident = (off + w_all + 2 * gk * p->x_bytes <= kSmemTotal) ? 1 : 0;
+  const int avail = kSmemTotal - 1024 - off;            // 1 KB slack: the M = 64/128 instruction reads past a short image
+  // resident weights or one image per stage: whichever keeps more gathered offsets in flight (memory latency is
+  // hidden by the depth of the ring); resident wins ties because it saves the re-streaming
+  int st_res = avail >= w_all ? (avail - w_all) / (gk * p->x_bytes) : 0;
+  int st_str = avail / (gk * (p->x_bytes + p->w_bytes));
+  if (st_res > kMaxStages) st_res = kMaxStages;
+  if (st_str > kMaxStages) st_str = kMaxStages;
+  p->w_resident = (st_res >= 2 && st_res >= st_str) ? 1 : 0;
+  int stages = p->w_resident ? st_res : st_str;
   if (p->w_resident) off += w_all;
   p->stage_off = off;
   const int stage_bytes = gk * (p->x_bytes + (p->w_resident ? 0 : p->w_bytes));
-  int stages = (kSmemTotal - off) / stage_bytes;
-  if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return false;
   const char* st_env = getenv("SPH_TC_STAGES");
   if (st_env && atoi(st_env) >= 2 && atoi(st_env) <= stages) stages = atoi(st_env);
   p->stages = stages;
-  *smem_bytes = off + stages * stage_bytes;
+  *smem_bytes = off + stages * stage_bytes + 1024;
   return true;
 }
 
@@ -438,7 +444,7 @@ void fill_shape(TcParams* p, int dtype, int K, int N, int out_esize) {
   p->row_bytes = K * dtype_bytes(dtype);
   p->kc = p->row_bytes / 16;
   p->x_bytes = p->kc * (int)kRowsLbo;   // kc chunk planes of 256 rows x 16 bytes (+ the bank skew)
-  p->w_bytes = p->MP * p->row_bytes;
+  p->w_bytes = N * p->row_bytes;       // image of the N real channels
   p->out_esize = out_esize;
 }
 
@@ -517,7 +523,7 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
 bool conv_tc_supported(int dtype, int kv, int K, int N) { return tc_shape_ok(dtype, kv, K, N); }
 
 int64_t packed_weight_bytes(int dtype, int kv, int K, int N) {
-  return (int64_t)kv * K * padded_m(N) * dtype_bytes(dtype);
+  return (int64_t)kv * K * N * dtype_bytes(dtype);
 }
 
 int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cudaStream_t st) {
@@ -525,15 +531,13 @@ int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cu
     set_error("pack_weight: unsupported dtype/shape");
     return SPH_ERR_UNSUPPORTED;
   }
-  const int MP = padded_m(N);
-  SPH_CUDA(cudaMemsetAsync(packed, 0, (size_t)packed_weight_bytes(dtype, kv, K, N), st));
   const int64_t total = (int64_t)kv * K * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)div_up64(total, threads);
   if (dtype == SPH_I8)
-    pack_weight_kernel<int8_t><<<blocks, threads, 0, st>>>((const int8_t*)w, kv, K, N, MP, (int8_t*)packed);
+    pack_weight_kernel<int8_t><<<blocks, threads, 0, st>>>((const int8_t*)w, kv, K, N, (int8_t*)packed);
   else
-    pack_weight_kernel<uint16_t><<<blocks, threads, 0, st>>>((const uint16_t*)w, kv, K, N, MP, (uint16_t*)packed);
+    pack_weight_kernel<uint16_t><<<blocks, threads, 0, st>>>((const uint16_t*)w, kv, K, N, (uint16_t*)packed);
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
