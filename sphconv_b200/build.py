@@ -38,6 +38,7 @@ def build(force=False, verbose=False):
     flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
     if verbose:
         flags += ["-Xptxas", "-v"]
+    flags += os.environ.get("SPH_NVCC_EXTRA", "").split()   # developer builds, e.g. -DSPH_TC_PROF
     objs = []
     procs = []
     for src in SOURCES:

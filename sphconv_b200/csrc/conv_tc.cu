@@ -108,6 +108,25 @@ __device__ __forceinline__ void stage_store16(uint8_t* dst, int row_pitch, int o
   }
 }
 
+// Developer instrumentation (-DSPH_TC_PROF): per-CTA cycle counts of each warp role and of its barrier waits.
+#ifdef SPH_TC_PROF
+__device__ long long g_tc_prof[256][12];
+#define SPH_PROF_BEGIN() long long prof_begin = clock64(), prof_t0 = 0, prof_acc[3] = {0, 0, 0}
+#define SPH_PROF_T0() prof_t0 = clock64()
+#define SPH_PROF_ADD(i) prof_acc[i] += clock64() - prof_t0
+#define SPH_PROF_END(base, pred)                                                     \
+  if ((pred) && blockIdx.x < 256) {                                                  \
+    g_tc_prof[blockIdx.x][(base) + 0] = clock64() - prof_begin;                      \
+    g_tc_prof[blockIdx.x][(base) + 1] = prof_acc[1];                                 \
+    g_tc_prof[blockIdx.x][(base) + 2] = prof_acc[2];                                 \
+  }
+#else
+#define SPH_PROF_BEGIN()
+#define SPH_PROF_T0()
+#define SPH_PROF_ADD(i)
+#define SPH_PROF_END(base, pred)
+#endif
+
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // KC = 16-byte chunks per gathered row (2, 4, 8, 16), I8 = int8 operands.  Both are compile-time so that the
@@ -218,6 +237,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     const uint32_t stage0_u = smem_u32(stage0);
     const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
 
+    SPH_PROF_BEGIN();
     int s = 0;
     uint32_t par = 1u;                            // parity to wait for on the empty barriers
     uint32_t bad = 0u;
@@ -229,7 +249,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       for (int k0 = 0; k0 < p.kv; k0 += GK) {
         // one lane polls: hundreds of threads polling one mbarrier serialise on it
         bool ok_w = true;
+        SPH_PROF_T0();
         if (lane == 0) ok_w = mbar_wait(empty0 + 8u * s, par, abort_flag);
+        SPH_PROF_ADD(1);
         if (__any_sync(0xffffffffu, !ok_w)) { dead = true; break; }   // also orders the other lanes behind the poll
         const uint32_t stage = stage0_u + (uint32_t)(s * stage_bytes);
         if (!p.w_resident && tid == 0) {
@@ -259,8 +281,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
               bad |= (uint32_t)(r[j] + 1) & (present ? 0u : ~0u);  // non-zero only for an id that is neither -1 nor valid
               const uint8_t* src = rows_c + (size_t)(present ? (uint32_t)r[j] : 0u) * row_bytes;
               const uint32_t sz = present ? 16u : 0u;
-              cp_async_16(dst0 + (uint32_t)j * 16u, src, sz);
-              if (PASSES == 2) cp_async_16(dst0 + (uint32_t)j * 16u + 8u * kRowsLbo, src + 128, sz);
+              // .ca: the three depth offsets of one (kh,kw) read nearly the same input rows a stage or two
+              // apart, and the slice of L1 that the shared-memory carve-out leaves catches most of the repeats
+              cp_async_16_ca(dst0 + (uint32_t)j * 16u, src, sz);
+              if (PASSES == 2) cp_async_16_ca(dst0 + (uint32_t)j * 16u + 8u * kRowsLbo, src + 128, sz);
             }
             trow += kTileRows;
           }
@@ -270,6 +294,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       }
       if (has_next && !dead) park_table();
     }
+    SPH_PROF_END(0, tid == 0);
     cp_async_wait_all();
     if (bad && p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
   } else if (warp == kMmaWarp) {
@@ -293,18 +318,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
       bool dead = false;
       if (p.w_resident) dead = !mbar_wait(smem_u32(&s_w_full), 0u, abort_flag);
+      SPH_PROF_BEGIN();
       int s = 0;
       uint32_t par = 0u;                                          // parity to wait for on the full barriers
       uint32_t x_lo = x_lo_first;
       for (int ti = 0; ti < my_tiles && !dead; ++ti) {
         const int buf = ti & 1;
+        SPH_PROF_T0();
         if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)ti >> 1) & 1u) ^ 1u, abort_flag)) break;
+        SPH_PROF_ADD(2);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTileRows);
         uint32_t accumulate = 0u;
         uint32_t w_lo = w_lo_res;
         for (int k0 = 0; k0 < p.kv; k0 += GK) {
+          SPH_PROF_T0();
           if (!mbar_wait(full0 + 8u * s, par, abort_flag)) { dead = true; break; }
+          SPH_PROF_ADD(1);
           tc_fence_after();
           const uint32_t wl0 = p.w_resident ? w_lo : x_lo + w_in_stage;
 #pragma unroll
@@ -327,6 +357,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
         }
         if (!dead) umma_commit(smem_u32(&s_acc_full[buf]));
       }
+      SPH_PROF_END(4, true);
     }
     __syncwarp();
   } else {
@@ -339,11 +370,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     const float sc = (has_oc && p.scale) ? __ldg(p.scale + oc) : 1.f;
     const float bi = (has_oc && p.bias) ? __ldg(p.bias + oc) : 0.f;
     const int row_pitch = p.N * p.out_esize;      // bytes of one output row; the staging buffer uses the same pitch
+    SPH_PROF_BEGIN();
     for (int ti = 0; ti < my_tiles; ++ti) {
       const int buf = ti & 1;
       const int64_t tile = (int64_t)blockIdx.x + (int64_t)ti * gridDim.x;
       bool ok = true;
+      SPH_PROF_T0();
       if (lane == 0) ok = mbar_wait(smem_u32(&s_acc_full[buf]), ((uint32_t)ti >> 1) & 1u, abort_flag, 128u);
+      SPH_PROF_ADD(1);
       if (__any_sync(0xffffffffu, !ok)) break;    // warp-uniform: tcgen05.ld is warp-wide
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTileRows);
@@ -372,6 +406,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_acc_empty[buf]));
     }
+    SPH_PROF_END(8, q == 0 && lane == 0);
   }
 
   // ---- wind down: every thread arrives here, also after an abort
@@ -543,3 +578,9 @@ int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cu
 }
 
 }  // namespace sph
+
+#ifdef SPH_TC_PROF
+extern "C" int sph_debug_tc_prof(long long* host_out /*[256*12]*/) {
+  return (int)cudaMemcpyFromSymbol(host_out, sph::g_tc_prof, sizeof(long long) * 256 * 12);
+}
+#endif
