@@ -57,9 +57,10 @@ __device__ __forceinline__ int find_row(const int* __restrict__ zi, const int* _
 }
 
 // One thread per input column: set the depth bits, then the running popcount.  The table must be zeroed.
+// row_col (optional) receives the column id of every row.
 __global__ void __launch_bounds__(256)
 build_colmask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, int64_t ncols, int words, int D,
-                     uint2* __restrict__ table, int* __restrict__ unsorted) {
+                     uint2* __restrict__ table, int* __restrict__ unsorted, int* __restrict__ row_col) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= ncols) return;
   const int s = col_start(zp, c), e = __ldg(zp + c);
@@ -72,6 +73,7 @@ build_colmask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, int
     if (z <= prev || z >= D) bad = true;
     prev = z;
     if (z >= 0 && z < D) row[z >> 5].x |= 1u << (z & 31);
+    if (row_col) row_col[r] = (int)c;
   }
   if (bad) *unsorted = 1;
   uint32_t run = 0;
@@ -88,7 +90,10 @@ __global__ void __launch_bounds__(kEmitThreads)
 emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, const int* __restrict__ out_zi,
                   const int* __restrict__ out_zp, Geom g, int64_t in_nnz, int64_t out_nnz, int tile_n_max,
                   int* __restrict__ rules, int* __restrict__ rule_size, int* __restrict__ nbr,
-                  int* __restrict__ nbr_t, ColMask cm, int* __restrict__ status) {
+                  int* __restrict__ nbr_t, ColMask cm, int* __restrict__ status, int fast_done) {
+  // fast_done: the row-parallel kernels below were launched for this call; they did the work unless
+  // they found a column stored out of depth order
+  if (fast_done && *cm.unsorted == 0) return;
   __shared__ int s_cnt[kMaxKV];
   __shared__ int s_rstart[kEmitMaxRanges];
   __shared__ int s_roff[kEmitMaxRanges + 1];
@@ -244,6 +249,198 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Row-parallel path (needs the input column masks and the neighbour table as an output).
+//  1. nbr_rows_kernel: one thread per OUTPUT row looks its KH*KW input columns up in the mask table and
+//     writes the KV entries nbr[k][row] (coalesced over rows) and, if asked, nbr_t[k][in] = row.
+//     The row's column id was parked in the last plane of nbr by the kernel that enumerated the rows
+//     (build_colmask_kernel for a submanifold layer, write_oz_idx_kernel for a strided one); the thread reads
+//     it first and overwrites it last.
+//  2. rule_lists_kernel: one warp per (tile, group of offsets) walks the tile's row ranges in list order
+//     (batch, tile row, row), reads nbr[k][row] and ballot-compacts the hits into rules[tile][k].
+// Both do nothing when a column was found out of depth order; emit_rules_kernel then does the work.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, Geom g, int64_t in_nnz,
+                int64_t out_nnz, int* nbr, int* __restrict__ nbr_t, ColMask cm) {
+  if (*cm.unsorted) return;
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= out_nnz) return;
+  const int c = nbr[(int64_t)(g.KV - 1) * out_nnz + r];
+  const int oy = c % g.oW;
+  const int t2 = c / g.oW;
+  const int ox = t2 % g.oH;
+  const int b = t2 / g.oH;
+  const int iz0 = __ldg(out_zi + r) * g.sD - g.pD;
+  int* dst = nbr + r;
+  int* dst_t = nbr_t;
+  for (int kh = 0; kh < g.KH; ++kh) {
+    const int ix = ox * g.sH - g.pH + kh;
+    for (int kw = 0; kw < g.KW; ++kw) {
+      const int iy = oy * g.sW - g.pW + kw;
+      const bool col_ok = ix >= 0 && ix < g.H && iy >= 0 && iy < g.W;
+      int cstart = 0;
+      const uint2* row = cm.table;
+      if (col_ok) {
+        const int64_t ci = ((int64_t)b * g.H + ix) * g.W + iy;
+        cstart = col_start(in_zp, ci);
+        row = cm.table + ci * cm.words;
+      }
+      int cur_w = -1;
+      uint2 e = make_uint2(0u, 0u);
+      for (int kd = 0; kd < g.KD; ++kd) {
+        const int iz = iz0 + kd;
+        int found = -1;
+        if (col_ok && iz >= 0 && iz < g.D) {
+          if ((iz >> 5) != cur_w) {
+            cur_w = iz >> 5;
+            e = __ldg(row + cur_w);
+          }
+          const uint32_t bit = 1u << (iz & 31);
+          if (e.x & bit) found = cstart + (int)e.y + __popc(e.x & (bit - 1u));
+        }
+        *dst = found;
+        dst += out_nnz;
+        if (nbr_t) {
+          if (found >= 0) dst_t[found] = (int)r;
+          dst_t += in_nnz;
+        }
+      }
+    }
+  }
+}
+
+constexpr int kListWarps = 8;
+constexpr int kListRanges = 128;   // (batch, tile row) ranges staged per pass
+constexpr int kListChunks = 8;     // 32-row chunks whose table reads are in flight together
+
+__global__ void __launch_bounds__(kListWarps * 32)
+rule_lists_kernel(const int* __restrict__ out_zp, Geom g, int64_t out_nnz, int tile_n_max, int kg, int n_kg,
+                  const int* __restrict__ nbr, int* __restrict__ rules, int* __restrict__ rule_size,
+                  const int* __restrict__ unsorted, int* __restrict__ status) {
+  __shared__ int s_rs[kListWarps][kListRanges];
+  __shared__ int s_off[kListWarps][kListRanges + 1];
+  if (*unsorted) return;
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int64_t item = (int64_t)blockIdx.x * kListWarps + wib;
+  if (item >= (int64_t)g.nTile * n_kg) return;
+  const int t = (int)(item / n_kg);
+  const int k_lo = (int)(item % n_kg) * kg;
+  const int nk = min(kg, g.KV - k_lo);          // <= 32: lane j keeps the running count of offset k_lo + j
+  const int th = t / g.tgW, tw = t % g.tgW;
+  const int ox0 = th * g.tH, oy0 = tw * g.tW;
+  const int tHe = min(g.tH, g.oH - ox0);
+  const int tWe = min(g.tW, g.oW - oy0);
+  const int R = g.B * tHe;                       // each (batch, tile row) is one contiguous run of output rows
+  const unsigned lt = (1u << lane) - 1u;
+  int* rs = s_rs[wib];
+  int* off = s_off[wib];
+  int cnt = 0;
+  bool overflow = false;
+  for (int rg = 0; rg < R; rg += kListRanges) {
+    const int nr = min(kListRanges, R - rg);
+    // ---- the runs of this group and the exclusive prefix of their lengths (list position -> row)
+    int carry = 0;
+    for (int base = 0; base < nr; base += 32) {
+      const int i = base + lane;
+      int s = 0, len = 0;
+      if (i < nr) {
+        const int rr = rg + i;
+        const int b = rr / tHe, dx = rr % tHe;
+        const int64_t c0 = ((int64_t)b * g.oH + (ox0 + dx)) * g.oW + oy0;
+        s = col_start(out_zp, c0);
+        len = __ldg(out_zp + c0 + tWe - 1) - s;
+      }
+      int incl = len;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      if (i < nr) {
+        rs[i] = s;
+        off[i + 1] = carry + incl;
+      }
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) off[0] = 0;
+    __syncwarp();
+    const int T = carry;
+    // list position -> row: positions only grow, so each lane walks the runs forward, keeping the bounds of
+    // its current run in registers
+    int cur = 0, cur_lo = 0, cur_hi = off[1], cur_rs = rs[0];
+    auto rows_for = [&](int p0, int* row) {
+#pragma unroll
+      for (int u = 0; u < kListChunks; ++u) {
+        const int p = p0 + u * 32 + lane;
+        row[u] = -1;
+        if (p < T) {
+          while (p >= cur_hi) {
+            ++cur;
+            cur_lo = cur_hi;
+            cur_hi = off[cur + 1];
+            cur_rs = rs[cur];
+          }
+          row[u] = cur_rs + (p - cur_lo);
+        }
+      }
+    };
+    auto load = [&](int j, const int* row, int* val) {
+      const int* plane = nbr + (int64_t)(k_lo + j) * out_nnz;
+#pragma unroll
+      for (int u = 0; u < kListChunks; ++u) val[u] = row[u] >= 0 ? __ldg(plane + row[u]) : -1;
+    };
+    // The table reads of the next step (next offset of this group of rows, or first offset of the next
+    // group) are issued before the current step is compacted, so their latency overlaps the stores.
+    int row[kListChunks], val[kListChunks];
+    if (T > 0) {
+      rows_for(0, row);
+      load(0, row, val);
+    }
+    for (int p0 = 0; p0 < T; p0 += 32 * kListChunks) {
+      int nrow[kListChunks];
+      const bool more = p0 + 32 * kListChunks < T;
+      for (int j = 0; j < nk; ++j) {
+        int nval[kListChunks];
+        if (j + 1 < nk) {
+          load(j + 1, row, nval);
+        } else if (more) {
+          rows_for(p0 + 32 * kListChunks, nrow);
+          load(0, nrow, nval);
+        }
+        int base = __shfl_sync(0xffffffffu, cnt, j);
+        int* lst = rules ? rules + ((int64_t)t * g.KV + (k_lo + j)) * 2 * tile_n_max : nullptr;
+#pragma unroll
+        for (int u = 0; u < kListChunks; ++u) {
+          const unsigned m = __ballot_sync(0xffffffffu, val[u] >= 0);
+          if (val[u] >= 0 && lst) {
+            const int slot = base + __popc(m & lt);
+            if (slot < tile_n_max) {
+              lst[slot] = val[u];
+              lst[tile_n_max + slot] = row[u];
+            } else {
+              overflow = true;
+            }
+          }
+          base += __popc(m);
+        }
+        if (lane == j) cnt = base;
+#pragma unroll
+        for (int u = 0; u < kListChunks; ++u) val[u] = nval[u];
+      }
+      if (more) {
+#pragma unroll
+        for (int u = 0; u < kListChunks; ++u) row[u] = nrow[u];
+      }
+    }
+    __syncwarp();   // the next group overwrites the staged runs
+  }
+  if (rule_size && lane < nk) rule_size[(int64_t)t * g.KV + k_lo + lane] = cnt;
+  if (overflow && status) atomicOr(status, SPH_STATUS_RULE_OVERFLOW);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Strided conv: output sparsity pattern.
 // Per output column a depth bitmask (ceil(oD/32) words) = OR over the KH*KW input columns that reach it
@@ -278,7 +475,9 @@ __device__ __forceinline__ int block_inclusive_scan(int v, int* s_warp /*[8]*/, 
 
 __global__ void __launch_bounds__(kScanThreads)
 strided_mask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, Geom g, int words, int64_t ncols,
-                    ColMask cm, uint32_t* __restrict__ mask, int* __restrict__ counts, int* __restrict__ blocksum) {
+                    ColMask cm, uint32_t* __restrict__ mask, int* __restrict__ counts, int* __restrict__ blocksum,
+                    int fast_done) {
+  if (fast_done && *cm.unsorted == 0) return;   // strided_bits_kernel + count_columns_kernel do the work
   __shared__ int s_warp[kScanThreads / 32];
   const int64_t c = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
   const bool use_mask = cm.table != nullptr && *cm.unsorted == 0;
@@ -343,6 +542,85 @@ strided_mask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, Geom
   if (threadIdx.x == 0) blocksum[blockIdx.x] = total;
 }
 
+// Bit-parallel form of the output pattern: one thread per (output column, 32-bin output word).  The input
+// words that can reach the output word are OR-ed over the KH*KW input columns first, then every output bin
+// tests its KD input bins in that union.  kBitsWords bounds the input words one output word can depend on.
+constexpr int kBitsWords = 8;
+
+__host__ __device__ inline bool strided_bits_ok(const Geom& g) {
+  return (31 * g.sD + g.KD - 1) / 32 + 2 <= kBitsWords;
+}
+
+__global__ void __launch_bounds__(256)
+strided_bits_kernel(Geom g, int words_out, int64_t ncols_out, ColMask cm, uint32_t* __restrict__ mask) {
+  if (*cm.unsorted) return;
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= ncols_out * words_out) return;
+  const int w = (int)(t % words_out);
+  const int64_t c = t / words_out;
+  const int oy = (int)(c % g.oW);
+  const int ox = (int)((c / g.oW) % g.oH);
+  const int b = (int)(c / ((int64_t)g.oW * g.oH));
+  const int oz_lo = w * 32;
+  const int n_bits = min(g.oD - oz_lo, 32);
+  const int iz_lo = max(0, oz_lo * g.sD - g.pD);
+  const int iz_hi = min(g.D - 1, (oz_lo + n_bits - 1) * g.sD - g.pD + g.KD - 1);
+  uint32_t out = 0;
+  if (iz_lo <= iz_hi) {
+    const int w_lo = iz_lo >> 5;
+    const int nw = (iz_hi >> 5) - w_lo + 1;
+    uint32_t u[kBitsWords];
+#pragma unroll
+    for (int j = 0; j < kBitsWords; ++j) u[j] = 0u;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      const int ix = ox * g.sH - g.pH + kh;
+      if (ix < 0 || ix >= g.H) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        const int iy = oy * g.sW - g.pW + kw;
+        if (iy < 0 || iy >= g.W) continue;
+        const uint2* row = cm.table + (((int64_t)b * g.H + ix) * g.W + iy) * cm.words + w_lo;
+#pragma unroll
+        for (int j = 0; j < kBitsWords; ++j)
+          if (j < nw) u[j] |= __ldg(row + j).x;
+      }
+    }
+    for (int bit = 0; bit < n_bits; ++bit) {
+      const int base = (oz_lo + bit) * g.sD - g.pD;
+      uint32_t hit = 0u;
+      for (int kd = 0; kd < g.KD; ++kd) {
+        const int iz = base + kd;
+        if (iz >= 0 && iz < g.D) {
+          const int wi = (iz >> 5) - w_lo;
+          uint32_t word = 0u;
+#pragma unroll
+          for (int j = 0; j < kBitsWords; ++j)
+            if (wi == j) word = u[j];
+          hit |= (word >> (iz & 31)) & 1u;
+        }
+      }
+      out |= hit << bit;
+    }
+  }
+  mask[t] = out;
+}
+
+// One thread per output column: bin count of the column, block-level sums for the scan.
+__global__ void __launch_bounds__(kScanThreads)
+count_columns_kernel(const uint32_t* __restrict__ mask, int words, int64_t ncols, const int* __restrict__ unsorted,
+                     int* __restrict__ counts, int* __restrict__ blocksum) {
+  if (*unsorted) return;
+  __shared__ int s_warp[kScanThreads / 32];
+  const int64_t c = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
+  int count = 0;
+  if (c < ncols) {
+    for (int w = 0; w < words; ++w) count += __popc(mask[c * words + w]);
+    counts[c] = count;
+  }
+  int total;
+  block_inclusive_scan(count, s_warp, &total);
+  if (threadIdx.x == 0) blocksum[blockIdx.x] = total;
+}
+
 // Single CTA: exclusive scan of the block sums in place, grand total to *out_total.
 __global__ void __launch_bounds__(kScanThreads)
 scan_blocksums_kernel(int* __restrict__ blocksum, int n, int* __restrict__ out_total) {
@@ -371,7 +649,7 @@ scan_columns_kernel(int* __restrict__ counts, int64_t ncols, const int* __restri
 
 __global__ void __launch_bounds__(kScanThreads)
 write_oz_idx_kernel(const uint32_t* __restrict__ mask, const int* __restrict__ oz_ptr, int words, int64_t ncols,
-                    int* __restrict__ oz_idx) {
+                    int* __restrict__ oz_idx, int* __restrict__ row_col) {
   const int64_t c = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
   if (c >= ncols) return;
   int pos = c == 0 ? 0 : oz_ptr[c - 1];
@@ -379,6 +657,7 @@ write_oz_idx_kernel(const uint32_t* __restrict__ mask, const int* __restrict__ o
     uint32_t m = mask[c * words + w];
     while (m) {
       int bit = __ffs(m) - 1;
+      if (row_col) row_col[pos] = (int)c;   // column id of the row, for nbr_rows_kernel
       oz_idx[pos++] = w * 32 + bit;
       m &= m - 1;
     }
@@ -411,8 +690,11 @@ __global__ void rules_to_nbr_kernel(const int* __restrict__ rules, const int* __
   }
 }
 
-// Input column masks pay off once columns hold more than a couple of voxels (deeper encoder levels).
-bool want_colmask(const Geom& g, int64_t in_nnz) { return in_nnz > 2 * (int64_t)g.B * g.H * g.W; }
+// The input column masks cost 8 bytes per (column, 32 depth bins); they are built unless the grid is so
+// empty that the table would dwarf the voxel list (then the per-column scans of emit_rules_kernel are used).
+bool want_colmask(const Geom& g, int64_t in_nnz) {
+  return (int64_t)g.B * g.H * g.W * div_up(g.D, 32) <= 8 * in_nnz;
+}
 
 size_t colmask_bytes(const Geom& g, int64_t in_nnz) {
   if (!want_colmask(g, in_nnz)) return 0;
@@ -422,7 +704,7 @@ size_t colmask_bytes(const Geom& g, int64_t in_nnz) {
 
 // Builds the table at `scratch` (layout: 256-byte header holding the unsorted flag, then the table).
 int build_colmask(const int* zi, const int* zp, const Geom& g, int64_t in_nnz, void* scratch, ColMask* cm,
-                  cudaStream_t st) {
+                  cudaStream_t st, int* row_col = nullptr) {
   cm->table = nullptr;
   cm->words = 0;
   cm->unsorted = nullptr;
@@ -434,22 +716,49 @@ int build_colmask(const int* zi, const int* zp, const Geom& g, int64_t in_nnz, v
   cm->words = words;
   cm->table = (const uint2*)((char*)scratch + 256);
   build_colmask_kernel<<<(unsigned)div_up64(ncols, 256), 256, 0, st>>>(zi, zp, ncols, words, g.D,
-                                                                        (uint2*)((char*)scratch + 256), (int*)scratch);
+                                                                        (uint2*)((char*)scratch + 256), (int*)scratch,
+                                                                        row_col);
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
 
+// Last plane of the neighbour table: where the row-enumerating kernel parks each output row's column id.
+int* parked_columns(const Geom& g, int* nbr, int64_t out_nnz) {
+  return nbr ? nbr + (int64_t)(g.KV - 1) * out_nnz : nullptr;
+}
+
+// rows_parked: the column ids of the output rows are in parked_columns() (row-parallel path possible).
 int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int* out_zp, const Geom& g,
                 int64_t in_nnz, int64_t out_nnz, int tnm, int* rules, int* rule_size, int* nbr, int* nbr_t,
-                const ColMask& cm, int fill_unused, int* status, cudaStream_t st) {
+                const ColMask& cm, bool rows_parked, int fill_unused, int* status, cudaStream_t st) {
   if (rules && fill_unused) {
     SPH_CUDA(cudaMemsetAsync(rules, 0xFF, (size_t)g.nTile * g.KV * 2 * (size_t)tnm * sizeof(int), st));
   }
   if (nbr_t && in_nnz > 0) {
     SPH_CUDA(cudaMemsetAsync(nbr_t, 0xFF, (size_t)g.KV * (size_t)in_nnz * sizeof(int), st));
   }
+  const bool fast = rows_parked && cm.table != nullptr && nbr != nullptr;
+  if (fast) {
+    if (out_nnz > 0) {
+      nbr_rows_kernel<<<(unsigned)div_up64(out_nnz, 256), 256, 0, st>>>(in_zp, out_zi, g, in_nnz, out_nnz, nbr, nbr_t,
+                                                                         cm);
+      SPH_LAUNCH_CHECK();
+    }
+    if (rule_size) {
+      // enough warps to fill the machine, at most 32 offsets per warp (one running count per lane)
+      const int64_t lists = (int64_t)g.nTile * g.KV;
+      int kg = (int)(lists / 20000);
+      kg = kg < 3 ? 3 : kg > 32 ? 32 : kg;
+      if (kg > g.KV) kg = g.KV;
+      const int n_kg = div_up(g.KV, kg);
+      const int64_t items = (int64_t)g.nTile * n_kg;
+      rule_lists_kernel<<<(unsigned)div_up64(items, kListWarps), kListWarps * 32, 0, st>>>(
+          out_zp, g, out_nnz, tnm, kg, n_kg, nbr, rules, rule_size, cm.unsorted, status);
+      SPH_LAUNCH_CHECK();
+    }
+  }
   emit_rules_kernel<<<g.nTile, kEmitThreads, 0, st>>>(in_zi, in_zp, out_zi, out_zp, g, in_nnz, out_nnz, tnm, rules,
-                                                      rule_size, nbr, nbr_t, cm, status);
+                                                      rule_size, nbr, nbr_t, cm, status, fast ? 1 : 0);
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
@@ -551,10 +860,10 @@ extern "C" int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, in
   SPH_CHECK_ARG((d_rules == nullptr) == (d_rule_size == nullptr), "rules and rule_size go together");
   SPH_CHECK_ARG(d_rules == nullptr || tile_n_max > 0, "tile_n_max must be positive");
   ColMask cm;
-  rc = build_colmask(d_z_idx, d_z_ptr, g, nnz, d_scratch, &cm, (cudaStream_t)stream);
+  rc = build_colmask(d_z_idx, d_z_ptr, g, nnz, d_scratch, &cm, (cudaStream_t)stream, parked_columns(g, d_nbr, nnz));
   if (rc != SPH_OK) return rc;
   return launch_emit(d_z_idx, d_z_ptr, d_z_idx, d_z_ptr, g, nnz, nnz, tile_n_max, d_rules, d_rule_size, d_nbr,
-                     nullptr, cm, fill_unused, d_status, (cudaStream_t)stream);
+                     nullptr, cm, /*rows_parked=*/d_nbr != nullptr, fill_unused, d_status, (cudaStream_t)stream);
 }
 
 // ---- allocation-free variant of sph_rules_subm ---------------------------------------------------
@@ -650,9 +959,18 @@ extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_
   rc = build_colmask(d_z_idx, d_z_ptr, g, nnz, l.colmask_bytes ? (char*)d_scratch + l.mask_bytes + l.blocksum_bytes : nullptr,
                      &cm, st);
   if (rc != SPH_OK) return rc;
+  const bool fast = cm.table != nullptr && strided_bits_ok(g);
+  if (fast) {
+    strided_bits_kernel<<<(unsigned)div_up64(l.ncols * l.words, 256), 256, 0, st>>>(g, l.words, l.ncols, cm, mask);
+    SPH_LAUNCH_CHECK();
+  }
   strided_mask_kernel<<<l.nblk, kScanThreads, 0, st>>>(d_z_idx, d_z_ptr, g, l.words, l.ncols, cm, mask, d_oz_ptr,
-                                                       blocksum);
+                                                       blocksum, fast ? 1 : 0);
   SPH_LAUNCH_CHECK();
+  if (fast) {
+    count_columns_kernel<<<l.nblk, kScanThreads, 0, st>>>(mask, l.words, l.ncols, cm.unsorted, d_oz_ptr, blocksum);
+    SPH_LAUNCH_CHECK();
+  }
   scan_blocksums_kernel<<<1, kScanThreads, 0, st>>>(blocksum, l.nblk, d_out_nnz);
   SPH_LAUNCH_CHECK();
   scan_columns_kernel<<<l.nblk, kScanThreads, 0, st>>>(d_oz_ptr, l.ncols, blocksum);
@@ -680,11 +998,13 @@ extern "C" int sph_rules_strided_fill(const int32_t* d_z_idx, const int32_t* d_z
   StridedScratch l = strided_layout(g, nnz);
   const uint32_t* mask = (const uint32_t*)d_scratch;
   if (out_nnz > 0) {
-    write_oz_idx_kernel<<<l.nblk, kScanThreads, 0, st>>>(mask, d_oz_ptr, l.words, l.ncols, d_oz_idx);
+    write_oz_idx_kernel<<<l.nblk, kScanThreads, 0, st>>>(mask, d_oz_ptr, l.words, l.ncols, d_oz_idx,
+                                                         parked_columns(g, d_nbr, out_nnz));
     SPH_LAUNCH_CHECK();
   }
   return launch_emit(d_z_idx, d_z_ptr, d_oz_idx, d_oz_ptr, g, nnz, out_nnz, tile_n_max, d_rules, d_rule_size,
-                     d_nbr, d_nbr_t, strided_colmask(g, nnz, l, d_scratch), fill_unused, d_status, st);
+                     d_nbr, d_nbr_t, strided_colmask(g, nnz, l, d_scratch), /*rows_parked=*/d_nbr != nullptr,
+                     fill_unused, d_status, st);
 }
 
 extern "C" int sph_rules_to_nbr(const int32_t* d_rules, const int32_t* d_rule_size, int32_t n_tile, int32_t kv,
