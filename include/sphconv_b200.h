@@ -109,7 +109,10 @@ int sph_rules_subm_static(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_
  *   d_oz_ptr    int32 [B,oH,oW], inclusive prefix like z_ptr
  *   d_out_nnz   int32 [1] on the device (= oz_ptr[-1])
  *   h_out_nnz   optional host pointer: when non-null the call synchronises `stream` and stores the
- *               count there (the same device->host read the reference does at rules.cu:461) */
+ *               count there (the same device->host read the reference does at rules.cu:461).  The kernel
+ *               hands the count over through a word of mapped pinned host memory, not a memcpy, so the read
+ *               does not queue behind bulk copies on the copy engines; the first such call on a device
+ *               allocates 1 KiB of pinned host memory that lives until the process ends. */
 int64_t sph_rules_strided_scratch_bytes(const sph_geom* g, int64_t nnz);
 int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
                             void* d_scratch, int32_t* d_oz_ptr, int32_t* d_out_nnz, int32_t* h_out_nnz,

@@ -9,6 +9,7 @@ from .modules import Sequential, SparseSequential, SphModule
 from .tensor import SparseConvTensor
 from .sphconv_cuda import config
 from ._capi import check_status
+from .pipeline import ScanPipeline
 
-__all__ = ["Conv3d", "SparseConv3d", "SubMConv3d", "Sequential", "SparseSequential", "SphModule",
+__all__ = ["ScanPipeline", "Conv3d", "SparseConv3d", "SubMConv3d", "Sequential", "SparseSequential", "SphModule",
            "SparseConvTensor", "config", "check_status"]

@@ -11,6 +11,8 @@
 //    (in,out) pairs to consecutive slots of its own list, so list order is deterministic
 //    (ascending output row inside a batch, batches in order) and no global atomics are used;
 //  * the same pass fills the neighbour tables nbr[k][out] / nbr_t[k][in] the convolution kernels read.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace sph {
@@ -623,7 +625,7 @@ count_columns_kernel(const uint32_t* __restrict__ mask, int words, int64_t ncols
 
 // Single CTA: exclusive scan of the block sums in place, grand total to *out_total.
 __global__ void __launch_bounds__(kScanThreads)
-scan_blocksums_kernel(int* __restrict__ blocksum, int n, int* __restrict__ out_total) {
+scan_blocksums_kernel(int* __restrict__ blocksum, int n, int* __restrict__ out_total, int* out_total_host) {
   __shared__ int s_warp[kScanThreads / 32];
   int carry = 0;
   for (int base = 0; base < n; base += kScanThreads) {
@@ -634,7 +636,13 @@ scan_blocksums_kernel(int* __restrict__ blocksum, int n, int* __restrict__ out_t
     if (i < n) blocksum[i] = carry + inc - v;
     carry += total;
   }
-  if (threadIdx.x == 0) *out_total = carry;
+  if (threadIdx.x == 0) {
+    *out_total = carry;
+    if (out_total_host) {          // mapped pinned host word: the host reads it after synchronising the stream
+      *(volatile int*)out_total_host = carry;
+      __threadfence_system();
+    }
+  }
 }
 
 // counts -> inclusive prefix (in place) using the scanned block sums.
@@ -936,6 +944,45 @@ ColMask strided_colmask(const Geom& g, int64_t nnz, const StridedScratch& l, con
 }
 }  // namespace
 
+// The host needs the output row count before it can size the outputs.  A cudaMemcpyAsync of those 4 bytes
+// would queue on the device-to-host copy engine behind whatever bulk copy another stream has in flight there
+// (measured: a result read-back of 90 MB on a side stream delayed it by milliseconds); instead the scan kernel
+// writes the count to a word of mapped pinned host memory.  A small ring of words per device, allocated on first
+// use, keeps concurrent calls apart.
+namespace {
+constexpr int kCountSlots = 256;
+struct CountRing {
+  int32_t* host = nullptr;
+  int32_t* dev = nullptr;
+};
+int count_slot(int32_t** host_word, int32_t** dev_word) {
+  constexpr int kMaxDevices = 64;
+  static CountRing rings[kMaxDevices];
+  static std::mutex mu;
+  static unsigned next = 0;
+  int dev = 0;
+  SPH_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error("device ordinal %d not supported", dev);
+    return SPH_ERR_LIMIT;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  CountRing& r = rings[dev];
+  if (r.host == nullptr) {
+    void* h = nullptr;
+    SPH_CUDA(cudaHostAlloc(&h, kCountSlots * sizeof(int32_t), cudaHostAllocMapped | cudaHostAllocPortable));
+    void* d = nullptr;
+    SPH_CUDA(cudaHostGetDevicePointer(&d, h, 0));
+    r.host = (int32_t*)h;
+    r.dev = (int32_t*)d;
+  }
+  const unsigned slot = next++ % kCountSlots;
+  *host_word = r.host + slot;
+  *dev_word = r.dev + slot;
+  return SPH_OK;
+}
+}  // namespace
+
 extern "C" int64_t sph_rules_strided_scratch_bytes(const sph_geom* s, int64_t nnz) {
   Geom g;
   int rc = make_geom(s, &g);
@@ -971,13 +1018,19 @@ extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_
     count_columns_kernel<<<l.nblk, kScanThreads, 0, st>>>(mask, l.words, l.ncols, cm.unsorted, d_oz_ptr, blocksum);
     SPH_LAUNCH_CHECK();
   }
-  scan_blocksums_kernel<<<1, kScanThreads, 0, st>>>(blocksum, l.nblk, d_out_nnz);
+  int32_t* host_word = nullptr;
+  int32_t* dev_word = nullptr;
+  if (h_out_nnz) {
+    rc = count_slot(&host_word, &dev_word);
+    if (rc != SPH_OK) return rc;
+  }
+  scan_blocksums_kernel<<<1, kScanThreads, 0, st>>>(blocksum, l.nblk, d_out_nnz, dev_word);
   SPH_LAUNCH_CHECK();
   scan_columns_kernel<<<l.nblk, kScanThreads, 0, st>>>(d_oz_ptr, l.ncols, blocksum);
   SPH_LAUNCH_CHECK();
   if (h_out_nnz) {
-    SPH_CUDA(cudaMemcpyAsync(h_out_nnz, d_out_nnz, sizeof(int), cudaMemcpyDeviceToHost, st));
     SPH_CUDA(cudaStreamSynchronize(st));
+    *h_out_nnz = *(volatile int32_t*)host_word;
   }
   return SPH_OK;
 }
