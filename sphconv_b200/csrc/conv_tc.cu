@@ -242,17 +242,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
     uint32_t par = 1u;                            // parity to wait for on the empty barriers
     uint32_t bad = 0u;
     bool dead = false;
+    const int batch = S >= 5 ? 3 : S >= 4 ? 2 : 1;   // stages acquired per poll (costs batch - 1 stages of run-ahead)
+    int credits = 0;
     for (int ti = 0; ti < my_tiles && !dead; ++ti) {
       const bool has_next = ti + 1 < my_tiles;
       if (has_next) load_table((int)blockIdx.x + (ti + 1) * (int)gridDim.x);
       const int* trow = tbl_row;
       for (int k0 = 0; k0 < p.kv; k0 += GK) {
-        // one lane polls: hundreds of threads polling one mbarrier serialise on it
-        bool ok_w = true;
-        SPH_PROF_T0();
-        if (lane == 0) ok_w = mbar_wait(empty0 + 8u * s, par, abort_flag);
-        SPH_PROF_ADD(1);
-        if (__any_sync(0xffffffffu, !ok_w)) { dead = true; break; }   // also orders the other lanes behind the poll
+        // One lane polls (hundreds of threads polling one mbarrier serialise on it), and only every `batch`
+        // stages: an mbarrier operation costs ~200 cycles of the polling thread, and the MMA thread releases the
+        // slots in order, so "the slot `batch - 1` stages ahead is free" implies the ones before it are too.
+        if (credits == 0) {
+          bool ok_w = true;
+          SPH_PROF_T0();
+          if (lane == 0) {
+            int sa = s + batch - 1;
+            uint32_t pa = par;
+            if (sa >= S) { sa -= S; pa ^= 1u; }
+            ok_w = mbar_wait(empty0 + 8u * sa, pa, abort_flag);
+          }
+          SPH_PROF_ADD(1);
+          if (__any_sync(0xffffffffu, !ok_w)) { dead = true; break; }   // also orders the other lanes behind the poll
+          credits = batch;
+        }
+        --credits;
         const uint32_t stage = stage0_u + (uint32_t)(s * stage_bytes);
         if (!p.w_resident && tid == 0) {
           const uint32_t bytes = (uint32_t)(min(GK, p.kv - k0) * p.w_bytes);
