@@ -2,15 +2,19 @@
 //
 // The sum over output rows is the MMA's K dimension.  Both operands are "MN-major" views of row tiles that sit
 // in shared memory in the same 8-row x 16-byte core-matrix layout the forward kernel gathers into:
-//   A = X_k^T  : M = iC (padded to 64 with zero chunk planes, or 128), K = 256 gathered rows of offset k
+//   A = [X_k0 | X_k1 | ...]^T : M = 128 = 128/iC kernel offsets side by side (the gathered tiles of a batch of
+//       offsets are adjacent in shared memory, and a tile is iC/8 chunk planes at a constant stride, so the batch is
+//       one operand of 16 planes), K = 256 output rows
 //   B = dY     : N = oC, K = the same 256 output rows (a plain contiguous copy, not a gather)
-//   D = dW[k]  : fp32 in TMEM, one accumulator per kernel offset.
-// TMEM holds 512 columns, i.e. floor(512/oC) accumulators, so the 27 offsets are split into groups and the grid
-// into (row-tile slice) x (offset group): a CTA keeps its group's accumulators in TMEM across ALL of its tiles and
-// adds them to the fp32 gradient once at the end with red.global.add.f32 (the reference writes a partial per
+//   D          : fp32 in TMEM, rows o*iC .. o*iC+iC-1 of a batch's accumulator are dW of its o-th offset.
+// An instruction costs the same ~60 cycles whether M is 32 or 128, and a tile needs 16 of them (K = 16 rows each)
+// per operand pair, so batching the offsets divides the instruction count by 128/iC.
+// TMEM holds 512 columns, i.e. floor(512/oC) batch accumulators; if the offsets need more they are split into groups
+// and the grid into (row-tile slice) x (offset group): a CTA keeps its accumulators in TMEM across ALL of its tiles
+// and adds them to the fp32 gradient once at the end with red.global.add.f32 (the reference writes a partial per
 // tile, [NTile,KV,iC,oC], and torch::sum's them, src/sphconv/rule_conv.cu:483-484,517).
 //
-// Warps 0-7 copy (dY tile once per tile, X_k tile once per offset), warp 8 issues the MMAs; the final flush is
+// Warps 0-7 copy (dY tile once per tile, one batch of X tiles per stage), warp 8 issues the MMAs; the final flush is
 // done by warps 0-3.  Same bounded waits and abort path as the forward kernel.
 #include <stdlib.h>
 
@@ -41,11 +45,10 @@ struct WgParams {
   int64_t n_rows, n_out;
   int kv, K, N;
   int kc_x, kc_y;       // 16-byte chunks per X row / dY row
-  int planes_x;         // chunk planes of an X tile (>= kc_x; the extra ones are zero and pad M to 64)
-  int MP;               // UMMA M: 64 or 128
+  int ob;               // offsets per batch = 128 / K: one stage, one accumulator, one MMA operand
   int is_bf16;
   int groups;           // offset groups
-  int per_group;        // offsets per group
+  int per_group;        // offsets per group (a multiple of ob)
   int slices;           // row-tile slices = gridDim.x / groups
   int num_tiles;
   int stages;
@@ -87,15 +90,6 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
     }
     mbar_init(smem_u32(&s_done), 1);
     mbar_init_fence();
-  }
-  // zero the padding planes of every X stage once: the gathers never touch them
-  if (p.planes_x > p.kc_x) {
-    for (int s = 0; s < S; ++s) {
-      uint4* z = (uint4*)(x_smem + (size_t)s * p.x_bytes + (size_t)p.kc_x * kPlane);
-      const int n16 = (p.planes_x - p.kc_x) * (int)kPlane / 16;
-      for (int i = tid; i < n16; i += kThreads) z[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    fence_proxy_async();   // generic-proxy stores that the tensor core will read
   }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&s_tmem_base), 512u);
@@ -142,15 +136,26 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
       copy_rows(smem_u32(y_smem + (size_t)yb * p.y_bytes), (const uint8_t*)p.dout, p.kc_y, (uint32_t)p.kc_y * 16u,
                 s_ids[warp][0], (unsigned)p.n_out);
       cp_async_arrive_noinc(smem_u32(&s_yfull[yb]));
-      // ---- one gathered X tile per offset of this CTA's group
-      for (int k = k_begin; k < k_end; ++k) {
-        const int nb = r < p.n_out ? __ldg(p.nbr + (int64_t)k * p.n_out + r) : -1;
+      // ---- one batch of gathered X tiles per stage (offsets past the group's end keep stale planes: they only
+      //      feed accumulator rows that are never flushed)
+      for (int kb = k_begin; kb < k_end; kb += p.ob) {
+        int nb[8];
+#pragma unroll
+        for (int o = 0; o < 8; ++o)
+          nb[o] = (o < p.ob && kb + o < k_end && r < p.n_out) ? __ldg(p.nbr + (int64_t)(kb + o) * p.n_out + r) : -1;
         if (lane == 0) ok = mbar_wait(smem_u32(&s_empty[s]), par, abort_flag);
         if (__any_sync(0xffffffffu, !ok)) { dead = true; break; }
-        s_ids[warp][1][lane] = nb;
-        __syncwarp();
-        copy_rows(smem_u32(x_smem + (size_t)s * p.x_bytes), (const uint8_t*)p.rows, p.kc_x, (uint32_t)p.kc_x * 16u,
-                  s_ids[warp][1], (unsigned)p.n_rows);
+        const uint32_t stage = smem_u32(x_smem + (size_t)s * p.x_bytes);
+#pragma unroll
+        for (int o = 0; o < 8; ++o) {
+          if (o < p.ob && kb + o < k_end) {      // uniform
+            __syncwarp();
+            s_ids[warp][1][lane] = nb[o];
+            __syncwarp();
+            copy_rows(stage + (uint32_t)(o * p.kc_x) * kPlane, (const uint8_t*)p.rows, p.kc_x, (uint32_t)p.kc_x * 16u,
+                      s_ids[warp][1], (unsigned)p.n_rows);
+          }
+        }
         cp_async_arrive_noinc(smem_u32(&s_full[s]));
         __syncwarp();
         if (++s == S) { s = 0; par ^= 1u; }
@@ -161,7 +166,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
     // ======================= MMA issuer =======================
     // both operands MN-major: SBO = stride between 8-element blocks along M/N (= chunk planes),
     // LBO = stride between 8-row groups along K (= 128 bytes); one instruction consumes 16 rows = 2 groups
-    const uint32_t idesc = make_idesc(1u, p.is_bf16 ? 1u : 0u, 1u, 1u, (uint32_t)p.MP, (uint32_t)p.N);
+    const uint32_t idesc = make_idesc(1u, p.is_bf16 ? 1u : 0u, 1u, 1u, 128u, (uint32_t)p.N);
+    const int nbatch = (nk + p.ob - 1) / p.ob;
     const uint64_t d0 = make_smem_desc(0u, 128u, kPlane);
     const uint64_t hi = d0 & 0xffffffff00000000ull;
     const uint32_t lo0 = (uint32_t)d0;
@@ -172,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
       const int yb = ti & 1;
       if (!mbar_wait(smem_u32(&s_yfull[yb]), ((uint32_t)ti >> 1) & 1u, abort_flag)) break;
       const uint32_t y_lo = lo0 + (smem_u32(y_smem + (size_t)yb * p.y_bytes) >> 4);
-      for (int k = 0; k < nk; ++k) {
+      for (int k = 0; k < nbatch; ++k) {
         if (!mbar_wait(smem_u32(&s_full[s]), par, abort_flag)) { dead = true; break; }
         fence_proxy_async();
         tc_fence_after();
@@ -198,14 +204,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
   // ======================= flush: warps 0-3 add the accumulators to the fp32 gradient =======================
   if (!s_abort && warp < 4 && my_tiles > 0) {
     const int q = warp;
-    const int ic = p.MP == 64 ? (lane < 16 ? 16 * q + lane : -1) : 32 * q + lane;
-    for (int k = 0; k < nk; ++k) {
+    const int m = 32 * q + lane;                    // accumulator row = TMEM lane (M = 128)
+    const int o = m / p.K, ic = m % p.K;            // offset inside the batch, input channel
+    const int nbatch = (nk + p.ob - 1) / p.ob;
+    for (int b = 0; b < nbatch; ++b) {
+      const int k = k_begin + b * p.ob + o;
       for (int c0 = 0; c0 < p.N; c0 += 16) {
         uint32_t raw[16];
-        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(k * p.N + c0), raw);
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * p.N + c0), raw);
         tmem_ld_wait();
-        if (ic >= 0 && ic < p.K) {
-          float* dst = p.dw + ((int64_t)(k_begin + k) * p.K + ic) * p.N + c0;
+        if (o < p.ob && k < k_end) {
+          float* dst = p.dw + ((int64_t)k * p.K + ic) * p.N + c0;
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (c0 + j < p.N) atomicAdd(dst + j, __uint_as_float(raw[j]));
@@ -236,14 +245,14 @@ bool wgrad_plan(WgParams* p, int dtype, int kv, int K, int N) {
   if (kv < 1 || kv > 64) return false;
   p->kv = kv; p->K = K; p->N = N;
   p->kc_x = xb / 16; p->kc_y = yb / 16;
-  p->MP = K <= 64 ? 64 : 128;
-  if (p->MP == 128 && N % 16 != 0) return false;
-  p->planes_x = p->MP / 8;
-  p->x_bytes = p->planes_x * (int)kPlane;
+  if (N % 16 != 0) return false;                      // M = 128 needs N in steps of 16
+  p->ob = 128 / K;                                   // K is 16, 32, 64 or 128
+  p->x_bytes = 16 * (int)kPlane;                     // ob tiles of K/8 planes = 16 planes
   p->y_bytes = p->kc_y * (int)kPlane;
-  const int acc_max = 512 / N;                      // accumulators that fit in TMEM
-  p->groups = (kv + acc_max - 1) / acc_max;
-  p->per_group = (kv + p->groups - 1) / p->groups;
+  const int nbatch = (kv + p->ob - 1) / p->ob;
+  const int acc_max = 512 / N;                       // batch accumulators that fit in TMEM
+  p->groups = (nbatch + acc_max - 1) / acc_max;
+  p->per_group = ((nbatch + p->groups - 1) / p->groups) * p->ob;
   p->y_off = 0;
   p->x_off = 2 * p->y_bytes;
   int stages = (kSmemTotal - p->x_off) / p->x_bytes;
