@@ -104,8 +104,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
   if (warp < kCopyWarps) {
     // ======================= copy warps =======================
     // lpr lanes copy the chunks of one row; a lane serves `lpr` consecutive rows of its warp's 32
+    // through_l1: the gathered X rows are re-read by the neighbouring depth offsets (keep them in L1); the dY tile
+    // is streamed once
     auto copy_rows = [&](uint32_t dst_tile, const uint8_t* base, int kc, uint32_t row_bytes, const int* ids,
-                         unsigned limit) {
+                         unsigned limit, bool through_l1) {
       const int lpr = kc < 8 ? kc : 8;
       const int passes = kc / lpr;
       const int l_chunk = lane % lpr;
@@ -116,13 +118,26 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
         const bool present = (unsigned)id < limit;
         const uint8_t* src = base + (size_t)(present ? (uint32_t)id : 0u) * row_bytes + l_chunk * 16;
         const uint32_t sz = present ? 16u : 0u;
-        for (int q = 0; q < passes; ++q) cp_async_16(dst0 + (uint32_t)j * 16u + (uint32_t)q * 8u * kPlane, src + q * 128, sz);
+        for (int q = 0; q < passes; ++q) {
+          if (through_l1) cp_async_16_ca(dst0 + (uint32_t)j * 16u + (uint32_t)q * 8u * kPlane, src + q * 128, sz);
+          else cp_async_16(dst0 + (uint32_t)j * 16u + (uint32_t)q * 8u * kPlane, src + q * 128, sz);
+        }
       }
     };
     __shared__ int s_ids[kCopyWarps][2][kRowsPerWarp];   // per warp: [0] output-row ids, [1] neighbour ids of one offset
     int s = 0;
     uint32_t par = 1u;
     bool dead = false;
+    // neighbour ids of one batch of offsets for this lane's row of tile ti (the table streams from HBM: the ids
+    // of the next batch are requested before the current batch is copied)
+    auto load_ids = [&](int ti, int kb, int (&nb)[8]) {
+      const int64_t rr = (int64_t)(slice + ti * p.slices) * kTileRows + warp * kRowsPerWarp + lane;
+#pragma unroll
+      for (int o = 0; o < 8; ++o)
+        nb[o] = (ti < my_tiles && o < p.ob && kb + o < k_end && rr < p.n_out) ? __ldg(p.nbr + (int64_t)(kb + o) * p.n_out + rr) : -1;
+    };
+    int nb[8], nb_next[8];
+    load_ids(0, k_begin, nb_next);
     for (int ti = 0; ti < my_tiles && !dead; ++ti) {
       const int tile = slice + ti * p.slices;
       const int64_t r = (int64_t)tile * kTileRows + warp * kRowsPerWarp + lane;
@@ -134,15 +149,15 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
       s_ids[warp][0][lane] = r < p.n_out ? (int)r : -1;
       __syncwarp();
       copy_rows(smem_u32(y_smem + (size_t)yb * p.y_bytes), (const uint8_t*)p.dout, p.kc_y, (uint32_t)p.kc_y * 16u,
-                s_ids[warp][0], (unsigned)p.n_out);
+                s_ids[warp][0], (unsigned)p.n_out, false);
       cp_async_arrive_noinc(smem_u32(&s_yfull[yb]));
       // ---- one batch of gathered X tiles per stage (offsets past the group's end keep stale planes: they only
       //      feed accumulator rows that are never flushed)
       for (int kb = k_begin; kb < k_end; kb += p.ob) {
-        int nb[8];
 #pragma unroll
-        for (int o = 0; o < 8; ++o)
-          nb[o] = (o < p.ob && kb + o < k_end && r < p.n_out) ? __ldg(p.nbr + (int64_t)(kb + o) * p.n_out + r) : -1;
+        for (int o = 0; o < 8; ++o) nb[o] = nb_next[o];
+        if (kb + p.ob < k_end) load_ids(ti, kb + p.ob, nb_next);
+        else load_ids(ti + 1, k_begin, nb_next);
         if (lane == 0) ok = mbar_wait(smem_u32(&s_empty[s]), par, abort_flag);
         if (__any_sync(0xffffffffu, !ok)) { dead = true; break; }
         const uint32_t stage = smem_u32(x_smem + (size_t)s * p.x_bytes);
@@ -153,7 +168,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
             s_ids[warp][1][lane] = nb[o];
             __syncwarp();
             copy_rows(stage + (uint32_t)(o * p.kc_x) * kPlane, (const uint8_t*)p.rows, p.kc_x, (uint32_t)p.kc_x * 16u,
-                      s_ids[warp][1], (unsigned)p.n_rows);
+                      s_ids[warp][1], (unsigned)p.n_rows, true);
           }
         }
         cp_async_arrive_noinc(smem_u32(&s_full[s]));
