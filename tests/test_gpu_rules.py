@@ -181,3 +181,58 @@ def test_bad_arguments_raise():
         ops.get_rules_subm(zi, zp, 1, [4, 4, 4], [2, 2, 2], [3, 3, 3], [1, 1, 1], [1, 1, 1], [1, 1, 1], [2, 2])  # shape
     with pytest.raises(RuntimeError):
         ops.get_rules(zi.cpu(), zp.cpu(), 1, [4, 4, 4], [2, 2, 2], [3, 3, 3], [2, 2, 2], [1, 1, 1], [1, 1, 1], [2, 2])
+
+
+@pytest.mark.parametrize("dens", [0.002, 0.05, 0.6])
+@pytest.mark.parametrize("subm", [True, False])
+def test_index_and_scan_paths_agree(dens, subm):
+    """Nearly empty grids take the per-column scan kernels (no column index is built), denser ones the row-parallel
+    kernels on the index; both must give the oracle's rules."""
+    B, shape, tile = 2, [12, 20, 96], [2, 2]
+    rng = np.random.default_rng(int(dens * 1000) + (7 if subm else 0))
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, dens, True)
+    ks, st, pd = ([3, 3, 3], [1, 1, 1], [1, 1, 1]) if subm else ([3, 3, 3], [2, 2, 2], [1, 1, 1])
+    _, _, _, oz_idx, oz_ptr, rules, rule_size = gpu_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    res = oracle_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    assert_rules_equal(res, oz_idx, oz_ptr.reshape(res["oz_ptr"].shape), rules, rule_size)
+    assert_tables_match(res, rules, z_idx.shape[0], oz_idx.shape[0])
+
+
+@pytest.mark.parametrize("ks,st,pd", [([7, 7, 7], [1, 1, 1], [3, 3, 3]), ([3, 3, 7], [2, 2, 6], [1, 1, 3]),
+                                      ([2, 2, 2], [2, 2, 2], [0, 0, 0]), ([3, 3, 5], [1, 2, 4], [1, 1, 2])])
+def test_large_kernels_and_strides(ks, st, pd):
+    """Kernel extents up to 7 and depth strides beyond what the bit-parallel pattern kernel handles."""
+    B, shape, tile = 2, [9, 11, 70], [2, 2]
+    rng = np.random.default_rng(sum(ks) * 10 + sum(st))
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.15, True)
+    subm = st == [1, 1, 1]
+    _, _, _, oz_idx, oz_ptr, rules, rule_size = gpu_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    res = oracle_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    assert_rules_equal(res, oz_idx, oz_ptr.reshape(res["oz_ptr"].shape), rules, rule_size)
+    assert_tables_match(res, rules, z_idx.shape[0], oz_idx.shape[0])
+
+
+@pytest.mark.parametrize("subm", [True, False])
+def test_tables_without_rule_lists(subm):
+    """config.materialize_rules = False: no rules / rule_size, the neighbour tables alone, still exact."""
+    B, shape, tile = 3, [10, 14, 40], [2, 2]
+    rng = np.random.default_rng(11)
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.2, True)
+    ks, st, pd = ([3, 3, 3], [1, 1, 1], [1, 1, 1]) if subm else ([3, 3, 3], [2, 2, 2], [1, 1, 1])
+    ops.config.materialize_rules = False
+    try:
+        with torch.enable_grad():
+            _, _, _, oz_idx, oz_ptr, tables, none = gpu_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    finally:
+        ops.config.materialize_rules = True
+    assert none is None
+    res = oracle_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    assert (oz_idx.cpu().numpy() == res["oz_idx"]).all()
+    KV = res["rule_size"].shape[1]
+    want = np.full((KV, oz_idx.shape[0]), -1, dtype=np.int64)
+    want[res["k"], res["out"]] = res["in"]
+    assert (tables.nbr.cpu().numpy() == want).all()
+    if not subm:
+        want_t = np.full((KV, z_idx.shape[0]), -1, dtype=np.int64)
+        want_t[res["k"], res["in"]] = res["out"]
+        assert (tables.nbr_t.cpu().numpy() == want_t).all()
