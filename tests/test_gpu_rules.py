@@ -236,3 +236,16 @@ def test_tables_without_rule_lists(subm):
         want_t = np.full((KV, z_idx.shape[0]), -1, dtype=np.int64)
         want_t[res["k"], res["in"]] = res["out"]
         assert (tables.nbr_t.cpu().numpy() == want_t).all()
+
+
+@pytest.mark.parametrize("subm", [True, False])
+def test_deep_grid(subm):
+    """More than 256 depth bins: the column index is built by the kernel that works in global memory."""
+    B, shape, tile = 2, [6, 10, 300], [2, 2]
+    rng = np.random.default_rng(5)
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.1, True)
+    ks, st, pd = ([3, 3, 3], [1, 1, 1], [1, 1, 1]) if subm else ([3, 3, 3], [2, 2, 2], [1, 1, 1])
+    _, _, _, oz_idx, oz_ptr, rules, rule_size = gpu_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    res = oracle_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    assert_rules_equal(res, oz_idx, oz_ptr.reshape(res["oz_ptr"].shape), rules, rule_size)
+    assert_tables_match(res, rules, z_idx.shape[0], oz_idx.shape[0])
