@@ -135,7 +135,7 @@ __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;"
 // streams, not the tensor pipe or the memory system, set the pace once the data path is asynchronous.
 template <int KC, bool I8>
 __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams p) {
-  constexpr int GK = KC == 2 ? 4 : KC == 4 ? 2 : 1;   // kernel offsets per pipeline stage
+  constexpr int GK = KC == 2 ? 4 : KC == 4 ? 3 : 1;   // kernel offsets per pipeline stage
   constexpr int LPR = KC < 8 ? KC : 8;           // lanes per row = rows per lane
   constexpr int PASSES = KC / LPR;               // 2 only for 256-byte rows
   constexpr int NMMA = KC / 2;                   // 32 bytes of K per instruction
@@ -464,7 +464,7 @@ bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   p->stg_off = off; off += kSubRows * p->N * p->out_esize;
   off = (off + 1023) & ~1023;
   p->w_off = off;
-  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? 2 : 1;   // kernel offsets per stage (must match the kernel's GK)
+  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? 3 : 1;   // kernel offsets per stage (must match the kernel's GK)
   const int w_all = kv * p->w_bytes;
   const int avail = kSmemTotal - 1024 - off;            // 1 KB slack: the M = 64/128 instruction reads past a short image
   // resident weights or one image per stage: whichever keeps more gathered offsets in flight (memory latency is
