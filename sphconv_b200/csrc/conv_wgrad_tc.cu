@@ -35,7 +35,7 @@ constexpr int kThreads = (kCopyWarps + 1) * 32;
 constexpr int kRowsPerWarp = kTileRows / kCopyWarps;
 constexpr uint32_t kPlane = kTileRows * 16 + 16;   // bytes of one chunk plane (256 rows x 16 B + bank skew)
 constexpr int kMaxStages = 6;
-constexpr int kSmemTotal = 227 * 1024 - 4096;   // dynamic shared memory next to the 3 KB static part
+constexpr int kSmemTotal = 227 * 1024 - 12288;   // dynamic shared memory next to the ~10 KB static part
 
 struct WgParams {
   const void* rows;     // X [n_rows, K]
@@ -57,7 +57,12 @@ struct WgParams {
   int* status;
 };
 
+// KCX = 16-byte chunks per gathered X row (2, 4, 8, 16); compile-time so that the gather of a batch is straight-line code.
+template <int KCX>
 __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) {
+  constexpr int OB = 16 / KCX;                   // offsets per batch (= p.ob)
+  constexpr int LPR = KCX < 8 ? KCX : 8;         // lanes per row = consecutive rows per lane
+  constexpr int PASSES = KCX / LPR;              // 2 only for 256-byte rows
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ __align__(8) uint64_t s_full[kMaxStages];
   __shared__ __align__(8) uint64_t s_empty[kMaxStages];
@@ -103,28 +108,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
 
   if (warp < kCopyWarps) {
     // ======================= copy warps =======================
-    // lpr lanes copy the chunks of one row; a lane serves `lpr` consecutive rows of its warp's 32
-    // through_l1: the gathered X rows are re-read by the neighbouring depth offsets (keep them in L1); the dY tile
-    // is streamed once
-    auto copy_rows = [&](uint32_t dst_tile, const uint8_t* base, int kc, uint32_t row_bytes, const int* ids,
-                         unsigned limit, bool through_l1) {
-      const int lpr = kc < 8 ? kc : 8;
-      const int passes = kc / lpr;
-      const int l_chunk = lane % lpr;
-      const int l_row0 = (lane / lpr) * lpr;
-      const uint32_t dst0 = dst_tile + (uint32_t)l_chunk * kPlane + (uint32_t)(warp * kRowsPerWarp + l_row0) * 16u;
-      for (int j = 0; j < lpr; ++j) {
-        const int id = ids[l_row0 + j];
-        const bool present = (unsigned)id < limit;
-        const uint8_t* src = base + (size_t)(present ? (uint32_t)id : 0u) * row_bytes + l_chunk * 16;
-        const uint32_t sz = present ? 16u : 0u;
-        for (int q = 0; q < passes; ++q) {
-          if (through_l1) cp_async_16_ca(dst0 + (uint32_t)j * 16u + (uint32_t)q * 8u * kPlane, src + q * 128, sz);
-          else cp_async_16(dst0 + (uint32_t)j * 16u + (uint32_t)q * 8u * kPlane, src + q * 128, sz);
-        }
-      }
-    };
-    __shared__ int s_ids[kCopyWarps][2][kRowsPerWarp];   // per warp: [0] output-row ids, [1] neighbour ids of one offset
+    __shared__ __align__(16) int s_ids[kCopyWarps][1 + 8][kRowsPerWarp];   // per warp: [1+o] neighbour ids of the batch's o-th offset
     int s = 0;
     uint32_t par = 1u;
     bool dead = false;
@@ -146,10 +130,21 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
       bool ok = true;
       if (lane == 0) ok = mbar_wait(smem_u32(&s_yempty[yb]), (((uint32_t)ti >> 1) & 1u) ^ 1u, abort_flag);
       if (__any_sync(0xffffffffu, !ok)) { dead = true; break; }
-      s_ids[warp][0][lane] = r < p.n_out ? (int)r : -1;
-      __syncwarp();
-      copy_rows(smem_u32(y_smem + (size_t)yb * p.y_bytes), (const uint8_t*)p.dout, p.kc_y, (uint32_t)p.kc_y * 16u,
-                s_ids[warp][0], (unsigned)p.n_out, false);
+      {
+        // the warp's 32 dY rows are one contiguous piece of memory: lanes walk it in 16-byte steps (coalesced) and
+        // drop each piece into its chunk plane
+        const int64_t row0 = (int64_t)tile * kTileRows + warp * kRowsPerWarp;
+        const uint8_t* src0 = (const uint8_t*)p.dout + row0 * (int64_t)(p.kc_y * 16);
+        const uint32_t ydst = smem_u32(y_smem + (size_t)yb * p.y_bytes) + (uint32_t)(warp * kRowsPerWarp) * 16u;
+        const int sh = 31 - __clz(p.kc_y);
+        for (int t = 0; t < p.kc_y; ++t) {
+          const int idx = t * 32 + lane;
+          const int rl = idx >> sh, ch = idx & (p.kc_y - 1);
+          const bool present = row0 + rl < p.n_out;
+          cp_async_16(ydst + (uint32_t)ch * kPlane + (uint32_t)rl * 16u, present ? src0 + (size_t)idx * 16 : (const uint8_t*)p.dout,
+                      present ? 16u : 0u);
+        }
+      }
       cp_async_arrive_noinc(smem_u32(&s_yfull[yb]));
       // ---- one batch of gathered X tiles per stage (offsets past the group's end keep stale planes: they only
       //      feed accumulator rows that are never flushed)
@@ -161,14 +156,42 @@ __global__ void __launch_bounds__(kThreads, 1) conv_wgrad_tc_kernel(WgParams p) 
         if (lane == 0) ok = mbar_wait(smem_u32(&s_empty[s]), par, abort_flag);
         if (__any_sync(0xffffffffu, !ok)) { dead = true; break; }
         const uint32_t stage = smem_u32(x_smem + (size_t)s * p.x_bytes);
+        __syncwarp();   // every lane has finished reading the previous batch's ids
 #pragma unroll
-        for (int o = 0; o < 8; ++o) {
-          if (o < p.ob && kb + o < k_end) {      // uniform
-            __syncwarp();
-            s_ids[warp][1][lane] = nb[o];
-            __syncwarp();
-            copy_rows(stage + (uint32_t)(o * p.kc_x) * kPlane, (const uint8_t*)p.rows, p.kc_x, (uint32_t)p.kc_x * 16u,
-                      s_ids[warp][1], (unsigned)p.n_rows, true);
+        for (int o = 0; o < OB; ++o) s_ids[warp][1 + o][lane] = nb[o];
+        __syncwarp();
+        {
+          const int l_chunk = lane % LPR;
+          const int l_row0 = (lane / LPR) * LPR;
+          const uint8_t* rows_c = (const uint8_t*)p.rows + l_chunk * 16;
+          const unsigned n_rows_u = (unsigned)p.n_rows;
+          const uint32_t dst_lane = stage + (uint32_t)l_chunk * kPlane + (uint32_t)(warp * kRowsPerWarp + l_row0) * 16u;
+#pragma unroll
+          for (int o = 0; o < OB; ++o) {
+            if (kb + o < k_end) {      // uniform
+              const int* ids = &s_ids[warp][1 + o][l_row0];
+              int r[LPR];
+              if (LPR == 8) {
+                const int4 a = *(const int4*)ids, b = *(const int4*)(ids + 4);
+                r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
+                r[4 % LPR] = b.x; r[5 % LPR] = b.y; r[6 % LPR] = b.z; r[7 % LPR] = b.w;
+              } else if (LPR == 4) {
+                const int4 a = *(const int4*)ids;
+                r[0] = a.x; r[1] = a.y; r[2 % LPR] = a.z; r[3 % LPR] = a.w;
+              } else {
+                const int2 a = *(const int2*)ids;
+                r[0] = a.x; r[1] = a.y;
+              }
+              const uint32_t dst0 = dst_lane + (uint32_t)(o * KCX) * kPlane;
+#pragma unroll
+              for (int j = 0; j < LPR; ++j) {
+                const bool present = (unsigned)r[j] < n_rows_u;
+                const uint8_t* src = rows_c + (size_t)(present ? (uint32_t)r[j] : 0u) * (uint32_t)(KCX * 16);
+                const uint32_t sz = present ? 16u : 0u;
+                cp_async_16_ca(dst0 + (uint32_t)j * 16u, src, sz);
+                if (PASSES == 2) cp_async_16_ca(dst0 + (uint32_t)j * 16u + 8u * kPlane, src + 128, sz);
+              }
+            }
           }
         }
         cp_async_arrive_noinc(smem_u32(&s_full[s]));
@@ -308,10 +331,21 @@ int conv_wgrad_tc(const void* rows, const void* dout, int dtype, int64_t n_rows,
   p.slices = slices;
   const int grid = slices * p.groups;
   const int smem_bytes = p.x_off + p.stages * p.x_bytes;
-  SPH_CUDA(cudaFuncSetAttribute(conv_wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-  conv_wgrad_tc_kernel<<<grid, kThreads, smem_bytes, st>>>(p);
+#define SPH_WG_LAUNCH(KCX_)                                                                                        \
+  do {                                                                                                           \
+    SPH_CUDA(cudaFuncSetAttribute(conv_wgrad_tc_kernel<KCX_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)); \
+    conv_wgrad_tc_kernel<KCX_><<<grid, kThreads, smem_bytes, st>>>(p);                                           \
+  } while (0)
+  switch (p.kc_x) {
+    case 2: SPH_WG_LAUNCH(2); break;
+    case 4: SPH_WG_LAUNCH(4); break;
+    case 8: SPH_WG_LAUNCH(8); break;
+    default: SPH_WG_LAUNCH(16); break;
+  }
+#undef SPH_WG_LAUNCH
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
 
 }  // namespace sph
+
