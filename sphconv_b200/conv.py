@@ -124,12 +124,9 @@ class Conv3d(Convolution):
         needs_grad = torch.is_grad_enabled() and (input.feature.requires_grad or self.weight.requires_grad)
         if needs_grad:
             profiling.current_tag = tag
+            # bias and activation run in the kernel's epilogue in training too (extension arguments of ConvFunction)
             out_feature = ConvFunction.apply(input.feature, weight, rules, rule_size, tile_grid_shape,
-                                             oz_idx.shape[0])
-            if bias is not None:
-                out_feature = out_feature + bias.to(out_feature.dtype)
-            if self.activation == 'relu':
-                out_feature = torch.relu(out_feature)
+                                             oz_idx.shape[0], bias, self.activation == 'relu')
         else:
             weight = self._cached_packed(weight)
             with profiling.section("conv:" + tag, iC=in_channels, oC=out_channels, n_in=input.feature.shape[0],

@@ -101,25 +101,41 @@ conv_wgrad_generic_kernel(const T* __restrict__ rows, const T* __restrict__ dout
   const int64_t r0 = (int64_t)blockIdx.x * kWgChunk;
   const int nr = (int)min((int64_t)kWgChunk, n_out - r0);
   const int tid = threadIdx.x, lane = tid & 31;
-  // deterministic compaction by warp 0
-  if (tid < 32) {
-    int n = 0;
-    for (int c = 0; c < nr; c += 32) {
-      int v = c + lane;
-      int i = v < nr ? __ldg(nbr + (int64_t)k * n_out + r0 + v) : -1;
-      if (i >= n_rows) {
-        if (status) atomicOr(status, SPH_STATUS_BAD_INDEX);
-        i = -1;
-      }
-      unsigned m = __ballot_sync(0xffffffffu, i >= 0);
-      if (i >= 0) {
-        int slot = n + __popc(m & ((1u << lane) - 1u));
-        s_in[slot] = i;
-        s_out[slot] = v;
-      }
-      n += __popc(m);
+  // deterministic compaction (ascending rows) by all warps: each counts the hits of its slice of the chunk, a prefix
+  // over the eight counts places the slices, then each warp writes its hits
+  __shared__ int s_wcnt[kWgThreads / 32];
+  constexpr int kSlice = kWgChunk / (kWgThreads / 32);
+  const int warp = tid >> 5;
+  const int c_begin = warp * kSlice, c_end = min(nr, c_begin + kSlice);
+  int cnt = 0;
+  for (int c = c_begin; c < c_end; c += 32) {
+    const int v = c + lane;
+    const int i = v < c_end ? __ldg(nbr + (int64_t)k * n_out + r0 + v) : -1;
+    cnt += __popc(__ballot_sync(0xffffffffu, i >= 0 && i < n_rows));
+  }
+  if (lane == 0) s_wcnt[warp] = cnt;
+  __syncthreads();
+  int n0 = 0;
+  for (int w = 0; w < warp; ++w) n0 += s_wcnt[w];
+  if (tid == 0) {
+    int t = 0;
+    for (int w = 0; w < kWgThreads / 32; ++w) t += s_wcnt[w];
+    s_n = t;
+  }
+  for (int c = c_begin; c < c_end; c += 32) {
+    const int v = c + lane;
+    int i = v < c_end ? __ldg(nbr + (int64_t)k * n_out + r0 + v) : -1;
+    if (i >= n_rows) {
+      if (status) atomicOr(status, SPH_STATUS_BAD_INDEX);
+      i = -1;
     }
-    if (lane == 0) s_n = n;
+    const unsigned m = __ballot_sync(0xffffffffu, i >= 0);
+    if (i >= 0) {
+      const int slot = n0 + __popc(m & ((1u << lane) - 1u));
+      s_in[slot] = i;
+      s_out[slot] = v;
+    }
+    n0 += __popc(m);
   }
   __syncthreads();
   const int n = s_n;

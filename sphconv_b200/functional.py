@@ -12,34 +12,50 @@ class ConvFunction(torch.autograd.Function):
     """Rule-driven sparse 3-D convolution (ref: sphconv/functional.py:12-78).
 
     forward(feature [NNZ,iC], weight [KV,iC,oC], rules, rule_size, tile_grid_shape, outNNZ) -> [outNNZ,oC]
-    backward returns (d_feature, d_weight, None, None, None, None)."""
+    backward returns (d_feature, d_weight, None, None, None, None).
+
+    Two optional trailing arguments (extensions): ``bias`` [oC] and ``relu``.  With them the kernel's epilogue
+    computes relu(acc + bias) in fp32 before the single rounding to the output dtype, and backward masks the incoming
+    gradient with (output > 0) and returns the bias gradient, so a training step needs no separate bias-add and
+    activation passes over the output."""
 
     @staticmethod
     def forward(ctx, feature: torch.Tensor, weight: torch.Tensor, rules, rule_size, tile_grid_shape: List[int],
-                outNNZ: int):
-        if isinstance(rules, torch.Tensor):
-            ctx.save_for_backward(feature, weight, rules, rule_size)
-            ctx.rule_obj = None
-        else:  # rule set generated without the padded tensor: keep the table object itself
-            ctx.save_for_backward(feature, weight)
-            ctx.rule_obj = rules
+                outNNZ: int, bias=None, relu: bool = False):
         ctx.tile_grid_shape = tile_grid_shape
         ctx.tag = profiling.current_tag
+        ctx.relu = bool(relu)
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
         with profiling.section("conv:" + ctx.tag, iC=weight.shape[1], oC=weight.shape[2], n_in=feature.shape[0],
                                n_out=int(outNNZ), esize=feature.element_size()):
             profiling.count_pairs("conv:" + ctx.tag, rules)
-            return rule_conv(feature, weight, rules, rule_size, outNNZ)
+            out = rule_conv(feature, weight, rules, rule_size, outNNZ,
+                            bias=None if bias is None else bias.detach().float(), relu=ctx.relu)
+        extra = (out,) if ctx.relu else ()
+        if isinstance(rules, torch.Tensor):
+            ctx.save_for_backward(feature, weight, rules, rule_size, *extra)
+            ctx.rule_obj = None
+        else:  # rule set generated without the padded tensor: keep the table object itself
+            ctx.save_for_backward(feature, weight, *extra)
+            ctx.rule_obj = rules
+        return out
 
     @staticmethod
     def backward(ctx, d_featureOut: torch.Tensor):
+        saved = ctx.saved_tensors
+        out = saved[-1] if ctx.relu else None
         if ctx.rule_obj is None:
-            feature, weight, rules, rule_size = ctx.saved_tensors
+            feature, weight, rules, rule_size = saved[:4]
         else:
-            feature, weight = ctx.saved_tensors
+            feature, weight = saved[:2]
             rules, rule_size = ctx.rule_obj, None
         # the ops take the [KV,oC,iC] transpose, as in the reference (sphconv/functional.py:70-74); this is
         # rule_conv_backward (src/sphconv/rule_conv.cu:577-597) spelled out so the two halves can be timed
         d_out = d_featureOut.contiguous()
+        if ctx.relu:
+            d_out = torch.where(out > 0, d_out, torch.zeros((), dtype=d_out.dtype, device=d_out.device))
+        d_bias = d_out.sum(0, dtype=torch.float32).to(ctx.bias_dtype) if ctx.has_bias else None
         meta = dict(iC=weight.shape[1], oC=weight.shape[2], n_in=feature.shape[0], n_out=d_out.shape[0],
                     esize=feature.element_size())
         with profiling.section("dgrad:" + ctx.tag, **meta):
@@ -47,7 +63,7 @@ class ConvFunction(torch.autograd.Function):
                                             ctx.tile_grid_shape, feature.shape[0])
         with profiling.section("wgrad:" + ctx.tag, **meta):
             d_weight = rule_conv_d_weight(feature, d_out, rules, rule_size).to(feature.dtype)
-        return d_feature, d_weight, None, None, None, None
+        return d_feature, d_weight, None, None, None, None, d_bias, None
 
 
 class ToDenseFunction(torch.autograd.Function):
