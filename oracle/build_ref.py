@@ -1,6 +1,6 @@
 """Builds the reference's own CUDA implementation of the path as a checker: oracle/_ref/sphconv_ref*.so.
 
-Sources are compiled where they lie in the reference tree (REFERENCE_ROOT, default /root/reference):
+Sources are compiled where they lie in the reference tree (the directory named by REFERENCE_ROOT):
 src/sphconv/rules.cu and src/sphconv/tensor.cu unmodified, plus - when a CUTLASS header tree is found -
 src/sphconv/rule_conv.cu.  The reference pins no CUTLASS version (its submodule directory is empty); the
 only copy on this machine is a 4.x tree whose MmaPipelined calls `iterator.clear_mask(bool)`, so the build
