@@ -365,7 +365,9 @@ def main():
             tf = flops / (ms * 1e-3) / 1e12
             gbs = byts / (ms * 1e-3) / 1e9
             k_ch, n_ch = (oC, iC) if kind == "dgrad" else (meta.get("k_ch", iC), meta.get("n_ch", oC))
-            uses_tc = kind != "wgrad" and bool(lib.sph_conv_uses_tensor_cores(dcode, k_ch, n_ch))
+            # wgrad has its own tensor-core kernel for the 16-bit types, with the same row-width rule
+            uses_tc = bool(lib.sph_conv_uses_tensor_cores(dcode, k_ch, n_ch)) and \
+                (kind != "wgrad" or dtype_name in ("fp16", "bf16"))
             layer_rows.append({"layer": name if kind != "conv" else name[5:], "ms": round(ms, 4), "pairs": pairs,
                                "tflops": round(tf, 2), "gbs": round(gbs, 1), "frac_tensor": round(tf / peaks["tflops"], 4),
                                "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "tensor_cores": uses_tc})
