@@ -174,6 +174,30 @@ int sph_conv_wgrad(const void* d_rows, const void* d_dout, int dtype, int64_t n_
                    int64_t n_out, int32_t kv, int32_t k_ch, int32_t n_ch, float* d_dweight, int zero_init,
                    int32_t* d_status, void* stream);
 
+/* ---- tensor operations on either side of the path: COO -> range-voxel, range-voxel <-> dense ----------------------
+ * Rows are moved as bytes (`row_bytes` = channels x element size), so every dtype takes the same entry points.
+ *
+ * sph_init_tensor  ref: init_tensor, src/sphconv/tensor.cu:78-127 (fillGridKernel, the sum/cumsum, reorderFeatureKernel).
+ *   d_indices      int32 [nnz,4] = (b, s0, s1, s2) per COO row, 16-byte aligned, no voxel listed twice
+ *   d_scratch      sph_init_tensor_scratch_bytes(B, shape) bytes
+ *   d_out_feature  [nnz, row_bytes]   d_z_idx int32 [nnz]   d_z_ptr int32 [B,s0,s1] (inclusive prefix)
+ *   d_permutation  int32 [nnz]: new row of COO row n (-1 for a row whose coordinates are out of range: status bit
+ *                  SPH_STATUS_BAD_INDEX).  Rows of a column come out in ascending depth (the reference's order is the
+ *                  arrival order of its atomics).
+ * sph_permute_rows ref: init_tensor_backward, tensor.cu:147-162, with gather = 1: d_dst[n] = d_src[permutation[n]];
+ *                  gather = 0 is the forward reorder d_dst[permutation[n]] = d_src[n].
+ * sph_to_dense     ref: to_dense / to_dense_backward, tensor.cu:222-309.  d_dense is [B,s0,s1,s2,row_bytes]; backward = 0
+ *                  copies every row to its voxel (the other voxels of d_dense are left as they are, as in the
+ *                  reference: the caller zero-fills), backward = 1 copies the voxels' values back into d_rows. */
+int64_t sph_init_tensor_scratch_bytes(int32_t B, const int32_t shape[3]);
+int sph_init_tensor(const void* d_feature, int32_t row_bytes, int64_t nnz, const int32_t* d_indices, int32_t B,
+                    const int32_t shape[3], void* d_scratch, void* d_out_feature, int32_t* d_z_idx,
+                    int32_t* d_z_ptr, int32_t* d_permutation, int32_t* d_status, void* stream);
+int sph_permute_rows(const void* d_src, int32_t row_bytes, int64_t n_rows, const int32_t* d_permutation, int gather,
+                     void* d_dst, void* stream);
+int sph_to_dense(void* d_rows, int32_t row_bytes, int64_t nnz, const int32_t* d_z_idx, const int32_t* d_z_ptr,
+                 int32_t B, const int32_t shape[3], void* d_dense, int backward, int32_t* d_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

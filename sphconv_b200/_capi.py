@@ -51,6 +51,10 @@ SIGNATURES = {
     "sph_conv_uses_tensor_cores": (cint, [cint, i32, i32]),
     "sph_conv_gather": (cint, [vp, cint, i64, vp, vp, vp, i64, i32, i32, i32, cint, vp, vp, cint, vp, cint, vp, vp]),
     "sph_conv_wgrad": (cint, [vp, vp, cint, i64, vp, i64, i32, i32, i32, vp, cint, vp, vp]),
+    "sph_init_tensor_scratch_bytes": (i64, [i32, c_i32p]),
+    "sph_init_tensor": (cint, [vp, i32, i64, vp, i32, c_i32p, vp, vp, vp, vp, vp, vp, vp]),
+    "sph_permute_rows": (cint, [vp, i32, i64, vp, cint, vp, vp]),
+    "sph_to_dense": (cint, [vp, i32, i64, vp, vp, i32, c_i32p, vp, cint, vp, vp]),
 }
 
 _lib = None

@@ -65,4 +65,8 @@ struct Geom {
 // Validates and converts; returns SPH_OK or an error code (message set).
 int make_geom(const sph_geom* g, Geom* out);
 
+// rules.cu: inclusive prefix over columns of the popcounts of per-column bit masks.
+int column_prefix_from_masks(const uint32_t* mask, int words, int64_t ncols, const int* zero_flag, int* prefix,
+                             int* blocksum, int* total_dev, cudaStream_t st);
+
 }  // namespace sph

@@ -773,6 +773,21 @@ int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int
 
 }  // namespace
 
+// Inclusive prefix over columns of the popcounts of per-column bit masks (shared with the tensor ops):
+// prefix[c] = number of set bits in columns 0..c; *total_dev = the grand total.  `zero_flag` points to a device int
+// that holds 0; `blocksum` needs ceil(ncols / 256) ints.
+int column_prefix_from_masks(const uint32_t* mask, int words, int64_t ncols, const int* zero_flag, int* prefix,
+                             int* blocksum, int* total_dev, cudaStream_t st) {
+  const int nblk = (int)div_up64(ncols, kScanThreads);
+  count_columns_kernel<<<nblk, kScanThreads, 0, st>>>(mask, words, ncols, zero_flag, prefix, blocksum);
+  SPH_LAUNCH_CHECK();
+  scan_blocksums_kernel<<<1, kScanThreads, 0, st>>>(blocksum, nblk, total_dev, nullptr);
+  SPH_LAUNCH_CHECK();
+  scan_columns_kernel<<<nblk, kScanThreads, 0, st>>>(prefix, ncols, blocksum);
+  SPH_LAUNCH_CHECK();
+  return SPH_OK;
+}
+
 int make_geom(const sph_geom* s, Geom* o) {
   SPH_CHECK_ARG(s != nullptr, "geometry is null");
   Geom g;

@@ -249,46 +249,76 @@ def rule_conv_backward(d_featureOut: torch.Tensor, feature: torch.Tensor, weight
     return [d_feature, d_weight]
 
 
-# ---- adjacent tensor ops (not on the accelerated path: COO <-> range-voxel, densify) -----------------
+# ---- tensor ops on either side of the path: COO -> range-voxel, range-voxel <-> dense -----------------------
 
-def _row_columns(zPtr: torch.Tensor):
-    zp = zPtr.reshape(-1).to(torch.int64)
-    counts = torch.diff(zp, prepend=zp.new_zeros(1))
-    return torch.repeat_interleave(torch.arange(zp.shape[0], device=zp.device), counts)
+def _shape3(spatialShape):
+    return (ctypes.c_int32 * 3)(*[int(v) for v in spatialShape])
 
 
 def init_tensor(feature: torch.Tensor, indicesBZYX: torch.Tensor, batchSize: int, spatialShape: List[int]):
     """ref: init_tensor, src/sphconv/tensor.cu:78-127.  COO (b, s0, s1, s2) -> range-voxel.
     Returns [feature', zIndices, zPtr, permutation] with permutation[n] = new row of input row n.
-    Rows inside a column are ordered by depth (the reference's order is atomics arrival order)."""
+    Rows inside a column are ordered by depth (the reference's order is atomics arrival order).  Any dtype."""
     C.require_cuda(feature, indicesBZYX)
-    H, W, D = [int(s) for s in spatialShape]
-    idx = indicesBZYX.to(torch.int64)
-    col = (idx[:, 0] * H + idx[:, 1]) * W + idx[:, 2]
-    order = torch.argsort(col * D + idx[:, 3], stable=True)
-    permutation = torch.empty_like(order)
-    permutation[order] = torch.arange(order.shape[0], device=order.device)
-    z_idx = idx[order, 3].to(torch.int32)
-    counts = torch.bincount(col, minlength=batchSize * H * W)
-    z_ptr = torch.cumsum(counts, 0).to(torch.int32).reshape(batchSize, H, W)
-    return [feature[order].contiguous(), z_idx, z_ptr, permutation.to(torch.int32)]
+    if indicesBZYX.dim() != 2 or indicesBZYX.shape[1] != 4 or indicesBZYX.is_floating_point():
+        raise RuntimeError("indices must be an integer tensor [NNZ, 4]")
+    if feature.dim() != 2 or feature.shape[0] != indicesBZYX.shape[0]:
+        raise RuntimeError("feature must be [NNZ, C] with one row per index")
+    lib = C.lib()
+    dev = feature.device
+    feature = feature.contiguous()
+    idx = indicesBZYX.to(torch.int32).contiguous()
+    nnz = feature.shape[0]
+    shape = _shape3(spatialShape)
+    out = torch.empty_like(feature)
+    z_idx = torch.empty((nnz,), dtype=torch.int32, device=dev)
+    z_ptr = torch.empty((int(batchSize), int(spatialShape[0]), int(spatialShape[1])), dtype=torch.int32, device=dev)
+    perm = torch.empty((nnz,), dtype=torch.int32, device=dev)
+    nbytes = C.check(lib.sph_init_tensor_scratch_bytes(int(batchSize), shape))
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        C.check(lib.sph_init_tensor(C.ptr(feature), feature.shape[1] * feature.element_size(), nnz, C.ptr(idx),
+                                    int(batchSize), shape, C.ptr(scratch), C.ptr(out), C.ptr(z_idx), C.ptr(z_ptr),
+                                    C.ptr(perm), C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+    return [out, z_idx, z_ptr, perm]
 
 
 def init_tensor_backward(d_featureOut: torch.Tensor, permutation: torch.Tensor) -> torch.Tensor:
     """ref: init_tensor_backward, src/sphconv/tensor.cu:147-162: d_feature[n] = d_featureOut[permutation[n]]."""
-    return d_featureOut[permutation.to(torch.int64)].contiguous()
+    C.require_cuda(d_featureOut, permutation)
+    d = d_featureOut.contiguous()
+    perm = permutation.contiguous()
+    if perm.dtype != torch.int32:
+        raise RuntimeError("permutation must be int32")
+    out = torch.empty_like(d)
+    with torch.cuda.device(d.device):
+        C.check(C.lib().sph_permute_rows(C.ptr(d), d.shape[1] * d.element_size(), d.shape[0], C.ptr(perm), 1, C.ptr(out),
+                                         C.stream_ptr(d.device)))
+    return out
 
 
 def to_dense(feature: torch.Tensor, zIndices: torch.Tensor, zPtr: torch.Tensor, D: int, out: torch.Tensor):
     """ref: to_dense, src/sphconv/tensor.cu:222-264.  Fills out [B,H,W,D,C] in place and returns it.
     The integer argument is unused, as in the reference kernel, which takes every size from `out`."""
-    col = _row_columns(zPtr)
-    out.view(-1, out.shape[3], out.shape[4])[col, zIndices.to(torch.int64)] = feature
+    C.require_cuda(feature, zIndices, zPtr, out)
+    if not out.is_contiguous() or out.dim() != 5 or out.dtype != feature.dtype or out.shape[4] != feature.shape[1]:
+        raise RuntimeError("out must be a contiguous [B,H,W,D,C] tensor of the feature dtype")
+    f = feature.contiguous()
+    with torch.cuda.device(f.device):
+        C.check(C.lib().sph_to_dense(C.ptr(f), f.shape[1] * f.element_size(), f.shape[0], C.ptr(zIndices.contiguous()),
+                                     C.ptr(zPtr.contiguous()), out.shape[0], _shape3(out.shape[1:4]), C.ptr(out), 0,
+                                     C.ptr(C.status_tensor(f.device)), C.stream_ptr(f.device)))
     return out
 
 
 def to_dense_backward(d_featureOut: torch.Tensor, zIndices: torch.Tensor, zPtr: torch.Tensor) -> torch.Tensor:
     """ref: to_dense_backward, src/sphconv/tensor.cu:266-309.  d_featureOut [B,H,W,D,C] -> [NNZ,C]."""
-    col = _row_columns(zPtr)
-    D, Cc = d_featureOut.shape[3], d_featureOut.shape[4]
-    return d_featureOut.reshape(-1, D, Cc)[col, zIndices.to(torch.int64)].contiguous()
+    C.require_cuda(d_featureOut, zIndices, zPtr)
+    d = d_featureOut.contiguous()
+    nnz = zIndices.shape[0]
+    out = torch.empty((nnz, d.shape[4]), dtype=d.dtype, device=d.device)
+    with torch.cuda.device(d.device):
+        C.check(C.lib().sph_to_dense(C.ptr(out), d.shape[4] * d.element_size(), nnz, C.ptr(zIndices.contiguous()),
+                                     C.ptr(zPtr.contiguous()), d.shape[0], _shape3(d.shape[1:4]), C.ptr(d), 1,
+                                     C.ptr(C.status_tensor(d.device)), C.stream_ptr(d.device)))
+    return out

@@ -90,3 +90,28 @@ def test_conv_matches_reference_kernels_fp32(ref, subm, iC, oC):
     for got, want in ((y, y_ref), (dx, dx_ref), (dw, dw_ref)):
         bound = 1e-4 * torch.clamp(want.abs().max(), min=1.0)
         assert (got - want).abs().max() <= bound
+
+
+def test_init_tensor_and_to_dense_match_reference_kernels(ref):
+    """The reference's init_tensor / to_dense (fp32 only; the order inside a column is its atomics' arrival order, so rows
+    are compared per column as sets and through the dense image)."""
+    rng = np.random.default_rng(17)
+    B, shape, C = 3, [7, 9, 40], 6
+    occ = rng.random((B, *shape)) < 0.2
+    idx = np.stack(np.nonzero(occ), axis=1).astype(np.int32)
+    rng.shuffle(idx)
+    feat = torch.as_tensor(rng.standard_normal((idx.shape[0], C)).astype(np.float32), device=DEV)
+    didx = torch.as_tensor(idx, device=DEV)
+    r_f, r_zi, r_zp, r_perm = ref.init_tensor(feat, didx, B, shape)
+    m_f, m_zi, m_zp, m_perm = ops.init_tensor(feat, didx, B, shape)
+    torch.cuda.synchronize()
+    assert torch.equal(r_zp.reshape(-1), m_zp.reshape(-1))
+    # both permutations place row n inside its column's range, and moved the row there
+    assert torch.equal(r_f[r_perm.long()], feat) and torch.equal(m_f[m_perm.long()], feat)
+    assert torch.equal(r_zi[r_perm.long()], didx[:, 3]) and torch.equal(m_zi[m_perm.long()], didx[:, 3])
+    r_dense = torch.zeros((B, *shape, C), device=DEV)
+    m_dense = torch.zeros((B, *shape, C), device=DEV)
+    ref.to_dense(r_f, r_zi, r_zp, shape[2], r_dense)
+    ops.to_dense(m_f, m_zi, m_zp, shape[2], m_dense)
+    torch.cuda.synchronize()
+    assert torch.equal(r_dense, m_dense)
