@@ -198,6 +198,13 @@ int sph_permute_rows(const void* d_src, int32_t row_bytes, int64_t n_rows, const
 int sph_to_dense(void* d_rows, int32_t row_bytes, int64_t nnz, const int32_t* d_z_idx, const int32_t* d_z_ptr,
                  int32_t B, const int32_t shape[3], void* d_dense, int backward, int32_t* d_status, void* stream);
 
+/* Backward of the fused epilogue relu(acc + bias) of sph_conv_gather (an extension: the reference applies no bias or
+ * activation).  d_dpre[r][c] = d_out[r][c] > 0 ? d_dout[r][c] : 0 (relu != 0; else a copy) and
+ * d_dbias[c] = sum over rows of d_dpre[r][c] (fp32 [channels], overwritten; may be null, as may d_dpre).
+ * dtype SPH_F32 / SPH_F16 / SPH_BF16; `channels` must divide 256. */
+int sph_epilogue_backward(const void* d_dout, const void* d_out, int dtype, int64_t n, int32_t channels, int relu,
+                          void* d_dpre, float* d_dbias, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,7 @@ SIGNATURES = {
     "sph_init_tensor": (cint, [vp, i32, i64, vp, i32, c_i32p, vp, vp, vp, vp, vp, vp, vp]),
     "sph_permute_rows": (cint, [vp, i32, i64, vp, cint, vp, vp]),
     "sph_to_dense": (cint, [vp, i32, i64, vp, vp, i32, c_i32p, vp, cint, vp, vp]),
+    "sph_epilogue_backward": (cint, [vp, vp, cint, i64, i32, cint, vp, vp, vp]),
 }
 
 _lib = None

@@ -208,3 +208,70 @@ extern "C" int sph_to_dense(void* d_rows, int32_t row_bytes, int64_t nnz, const 
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
+
+// ---- backward of the fused epilogue relu(acc + bias): gradient mask and bias gradient in one pass ---------------
+namespace sph {
+namespace {
+
+__device__ __forceinline__ float ld_f(const float* p, int64_t i) { return p[i]; }
+__device__ __forceinline__ float ld_f(const __half* p, int64_t i) { return __half2float(p[i]); }
+__device__ __forceinline__ float ld_f(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void st_f(float* p, int64_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void st_f(__half* p, int64_t i, float v) { p[i] = __float2half_rn(v); }
+__device__ __forceinline__ void st_f(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+constexpr int kEpiThreads = 256;
+
+// d_pre[r][c] = out[r][c] > 0 ? d_out[r][c] : 0 (relu) or d_out (no relu); d_bias[c] += sum_r d_pre[r][c].
+// A thread stays on one channel (C divides the block size), walks rows with a grid stride and keeps its sum in a
+// register; sums of equal channels meet in shared memory, one atomic per channel and block.
+template <typename T>
+__global__ void __launch_bounds__(kEpiThreads)
+epilogue_backward_kernel(const T* __restrict__ d_out, const T* __restrict__ out, int64_t n, int C, int relu,
+                         T* __restrict__ d_pre, float* __restrict__ d_bias) {
+  __shared__ float s_sum[kEpiThreads];
+  const int c = threadIdx.x % C;
+  const int rows_per_block = kEpiThreads / C;
+  float sum = 0.f;
+  for (int64_t r = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / C; r < n; r += (int64_t)gridDim.x * rows_per_block) {
+    const int64_t i = r * C + c;
+    float g = ld_f(d_out, i);
+    if (relu && !(ld_f(out, i) > 0.f)) g = 0.f;
+    if (d_pre) st_f(d_pre, i, g);
+    sum += g;
+  }
+  if (d_bias) {
+    s_sum[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x < C) {
+      float t = 0.f;
+      for (int j = threadIdx.x; j < kEpiThreads; j += C) t += s_sum[j];
+      atomicAdd(d_bias + threadIdx.x, t);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace sph
+
+extern "C" int sph_epilogue_backward(const void* d_dout, const void* d_out, int dtype, int64_t n, int32_t channels,
+                                     int relu, void* d_dpre, float* d_dbias, void* stream) {
+  SPH_CHECK_ARG(n >= 0 && channels > 0, "bad sizes");
+  SPH_CHECK_ARG(dtype == SPH_F32 || dtype == SPH_F16 || dtype == SPH_BF16, "unsupported dtype");
+  SPH_CHECK_ARG(channels <= kEpiThreads && kEpiThreads % channels == 0, "channel count must divide 256");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (d_dbias) SPH_CUDA(cudaMemsetAsync(d_dbias, 0, (size_t)channels * sizeof(float), st));
+  if (n == 0) return SPH_OK;
+  SPH_CHECK_ARG(d_dout && (!relu || d_out) && (d_dpre || d_dbias), "null pointer");
+  const int rows_per_block = kEpiThreads / channels;
+  int64_t blocks = div_up64(n, (int64_t)rows_per_block * 8);      // ~8 rows per thread
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  switch (dtype) {
+    case SPH_F32: epilogue_backward_kernel<float><<<(unsigned)blocks, kEpiThreads, 0, st>>>((const float*)d_dout, (const float*)d_out, n, channels, relu, (float*)d_dpre, d_dbias); break;
+    case SPH_F16: epilogue_backward_kernel<__half><<<(unsigned)blocks, kEpiThreads, 0, st>>>((const __half*)d_dout, (const __half*)d_out, n, channels, relu, (__half*)d_dpre, d_dbias); break;
+    default: epilogue_backward_kernel<__nv_bfloat16><<<(unsigned)blocks, kEpiThreads, 0, st>>>((const __nv_bfloat16*)d_dout, (const __nv_bfloat16*)d_out, n, channels, relu, (__nv_bfloat16*)d_dpre, d_dbias); break;
+  }
+  SPH_LAUNCH_CHECK();
+  return SPH_OK;
+}

@@ -4,8 +4,8 @@ from typing import List
 import torch
 
 from . import profiling
-from .sphconv_cuda import (init_tensor, init_tensor_backward, rule_conv, rule_conv_d_feature, rule_conv_d_weight,
-                           to_dense, to_dense_backward)
+from .sphconv_cuda import (epilogue_backward, init_tensor, init_tensor_backward, rule_conv, rule_conv_d_feature,
+                           rule_conv_d_weight, to_dense, to_dense_backward)
 
 
 class ConvFunction(torch.autograd.Function):
@@ -53,9 +53,11 @@ class ConvFunction(torch.autograd.Function):
         # the ops take the [KV,oC,iC] transpose, as in the reference (sphconv/functional.py:70-74); this is
         # rule_conv_backward (src/sphconv/rule_conv.cu:577-597) spelled out so the two halves can be timed
         d_out = d_featureOut.contiguous()
-        if ctx.relu:
-            d_out = torch.where(out > 0, d_out, torch.zeros((), dtype=d_out.dtype, device=d_out.device))
-        d_bias = d_out.sum(0, dtype=torch.float32).to(ctx.bias_dtype) if ctx.has_bias else None
+        d_bias = None
+        if ctx.relu or ctx.has_bias:    # gradient mask and bias gradient in one pass over the rows
+            d_out, d_bias = epilogue_backward(d_out, out, ctx.relu, ctx.has_bias)
+            if d_bias is not None:
+                d_bias = d_bias.to(ctx.bias_dtype)
         meta = dict(iC=weight.shape[1], oC=weight.shape[2], n_in=feature.shape[0], n_out=d_out.shape[0],
                     esize=feature.element_size())
         with profiling.section("dgrad:" + ctx.tag, **meta):

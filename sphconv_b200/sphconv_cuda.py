@@ -322,3 +322,25 @@ def to_dense_backward(d_featureOut: torch.Tensor, zIndices: torch.Tensor, zPtr: 
                                      C.ptr(zPtr.contiguous()), d.shape[0], _shape3(d.shape[1:4]), C.ptr(d), 1,
                                      C.ptr(C.status_tensor(d.device)), C.stream_ptr(d.device)))
     return out
+
+
+def epilogue_backward(d_out: torch.Tensor, out: Optional[torch.Tensor], relu: bool, need_bias: bool):
+    """Backward of the fused epilogue relu(acc + bias) (extension, no reference counterpart): returns
+    (d_pre, d_bias fp32 [C] or None) with d_pre = d_out masked by (out > 0) when `relu`."""
+    d_out = d_out.contiguous()
+    out = None if out is None else out.contiguous()
+    C.require_cuda(d_out, out)
+    n, ch = d_out.shape
+    if d_out.dtype not in (torch.float32, torch.float16, torch.bfloat16) or 256 % ch != 0:
+        d_pre = torch.where(out > 0, d_out, torch.zeros((), dtype=d_out.dtype, device=d_out.device)) if relu else d_out
+        return d_pre, (d_pre.sum(0, dtype=torch.float32) if need_bias else None)
+    dev = d_out.device
+    d_pre = torch.empty_like(d_out) if relu else None
+    d_bias = torch.empty((ch,), dtype=torch.float32, device=dev) if need_bias else None
+    if d_pre is None and d_bias is None:
+        return d_out, None
+    with torch.cuda.device(dev):
+        C.check(C.lib().sph_epilogue_backward(C.ptr(d_out), C.ptr(out) if relu else None,
+                                              C.DTYPE_CODE[d_out.dtype], n, ch, int(bool(relu)), C.ptr(d_pre),
+                                              C.ptr(d_bias), C.stream_ptr(dev)))
+    return (d_pre if relu else d_out), d_bias

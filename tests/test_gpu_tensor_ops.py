@@ -60,3 +60,20 @@ def test_empty_and_bad_coordinates():
     with pytest.raises(RuntimeError):      # SPH_STATUS_BAD_INDEX is reported (and cleared) by the status read
         check_status()
     assert check_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("C,n", [(16, 1000), (64, 12345), (32, 7), (128, 300)])
+def test_epilogue_backward(dtype, C, n):
+    """Gradient mask of relu(acc + bias) and the bias gradient in one pass, against the torch expressions."""
+    g = torch.Generator(device=DEV).manual_seed(C + n)
+    out = torch.relu(torch.randn((n, C), generator=g, device=DEV)).to(dtype)
+    d_out = torch.randn((n, C), generator=g, device=DEV).to(dtype)
+    for relu in (True, False):
+        d_pre, d_bias = ops.epilogue_backward(d_out, out, relu, True)
+        want = torch.where(out > 0, d_out, torch.zeros((), dtype=dtype, device=DEV)) if relu else d_out
+        assert torch.equal(d_pre, want)
+        ref = want.double().sum(0)
+        assert torch.allclose(d_bias.double(), ref, rtol=1e-4, atol=1e-3 * max(1.0, float(ref.abs().max())))
+    d_pre, d_bias = ops.epilogue_backward(d_out, out, True, False)
+    assert d_bias is None and torch.equal(d_pre, torch.where(out > 0, d_out, torch.zeros((), dtype=dtype, device=DEV)))
