@@ -2,9 +2,9 @@
 //
 //   out[r,:] = epilogue( sum_k rows[nbr[k][r], :] @ W[k] )          r in [0, n_out)
 //
-// A tcgen05.mma costs about 200 SM cycles to issue whatever its shape (measured on B200 for every
-// M in {64,128}, N in 16..256), so the instruction has to be as large as the problem allows.  The
-// channel counts here are small (<= 128) and the row count is huge, so the product is computed
+// A tcgen05.mma takes 55-128 SM cycles whatever its shape below M = 128, N = 256 (measured on B200), so the
+// instruction has to be as large as the problem allows.  The channel counts here are small (<= 128) and
+// the row count is huge, so the product is computed
 // transposed:  D^T[oC x 256 rows] += W[k]^T[oC x iC] * X_k^T[iC x 256 rows]
 //   A operand = W[k]^T, M = oC padded to 64 or 128, K-major, pre-packed once per weight;
 //   B operand = the 256 gathered neighbour rows of offset k, N = 256, K-major: each row is copied with
@@ -17,10 +17,10 @@
 // (the reference does a read-modify-write of the output per 8 pairs, include/sphconv/iterator.cu.h:1467-1625,
 // driven by the per-tile loop of include/sphconv/rule_conv_kernel.cu.h:91-153).
 //
-// Warp roles (416 threads): warps 0-7 gather (32 rows of the tile each), warp 8 issues the MMAs (one
-// thread) and owns TMEM, warps 9-12 run the epilogue.  Stages are handed over with mbarriers;
-// the accumulator is double buffered in TMEM (2 x 256 columns) so the epilogue of tile i overlaps the
-// MMAs of tile i+1.
+// Warp roles (416 threads): warps 0-7 gather, as two teams of four that fill alternate pipeline stages (a
+// warp gathers 64 rows of its team's stage), warp 8 issues the MMAs (one thread) and owns TMEM, warps 9-12 run
+// the epilogue.  Stages are handed over with mbarriers; the accumulator is double buffered in TMEM
+// (2 x 256 columns) so the epilogue of tile i overlaps the MMAs of tile i+1.
 //
 // Shared-memory operand layout (no swizzle): 8-row x 16-byte core matrices of 128 contiguous bytes;
 // rows: core (row group g, chunk c) at c*4112 + g*128; weights: core (channel group gn, chunk c) at
@@ -39,11 +39,13 @@ using namespace tc;
 
 constexpr int kTcMaxKV = 32;        // kernel volume the tensor-core kernel handles (3x3x3 = 27)
 constexpr int kTileRows = 256;      // output rows per tile = UMMA N
-constexpr int kProducerWarps = 8;    // gather warps; each owns 256 / 8 = 32 rows of the tile
+#ifndef SPH_TC_PRODUCER_WARPS
+#define SPH_TC_PRODUCER_WARPS 8
+#endif
+constexpr int kProducerWarps = SPH_TC_PRODUCER_WARPS;    // gather warps
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kTcThreads = (kProducerWarps + 1 + 4) * 32;
-constexpr int kRowsPerWarp = kTileRows / kProducerWarps;
 constexpr int kSubRows = 64;        // rows transposed through shared memory at a time in the epilogue
 constexpr int kMaxStages = 8;
 constexpr int kSmemTotal = 227 * 1024 - 2048;   // dynamic shared memory available next to the static part
@@ -62,6 +64,7 @@ struct TcParams {
   int row_bytes;        // K * elem bytes
   int kc;               // 16-byte chunks per gathered row
   int stages;
+  int groups;           // gather-warp teams (2); team q fills stages q, q + 2, ...
   int w_resident;       // all KV weight images live in shared memory
   int x_bytes, w_bytes; // per-offset operand bytes: gathered rows, weight image
   int flip_k;
@@ -154,7 +157,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   const int lane = tid & 31;
   const int S = p.stages;
   const int stage_bytes = GK * ((int)X_BYTES + (p.w_resident ? 0 : p.w_bytes));
-  int* s_tbl = (int*)(smem + p.tbl_off);          // [kv][256] neighbour rows of the current tile
+  int* s_tbl = (int*)(smem + p.tbl_off);          // per producer warp: neighbour rows of its share of one stage
   uint8_t* s_stg = smem + p.stg_off;              // [64][N] epilogue transpose buffer
   uint8_t* w_smem = smem + p.w_off;               // resident weight images (if any)
   uint8_t* stage0 = smem + p.stage_off;
@@ -163,7 +166,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(&s_full[s]), kProducerThreads + (p.w_resident ? 0 : 1));
+      mbar_init(smem_u32(&s_full[s]), 32 * (kProducerWarps / p.groups) + (p.w_resident ? 0 : 1));
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -188,11 +191,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
 
   if (warp < kProducerWarps) {
     // ======================= gather producers =======================
-    // The per-stage instruction stream of a producer warp sits on the pipeline's critical path, so it
-    // is kept to: one barrier poll, a shared-memory read of the neighbour row id, kc cp.async per row,
-    // one arrive.  The neighbour-table entries of the NEXT tile are loaded into registers while the
-    // current tile is gathered and parked in shared memory at the tile boundary, so no global-load
-    // latency sits on that path.
+    // Stage ownership: the gather warps form two teams; team q fills pipeline stages q, q + 2, ... (all 256 rows
+    // of the stage, 64 per warp).  The arrive that ties a stage's barrier to the completion of a thread's copies
+    // (cp.async.mbarrier.arrive.noinc) holds back the later memory instructions of that warp until the copies
+    // have landed; with every warp working on every stage, the copies of stage f+1 could not be issued while
+    // those of stage f were landing.  With ownership one team issues while the other team's copies land.
+    // Everything below is compile-time (team count, rows per warp and lane), so a stage is straight-line code.
+    constexpr int G = 2;                           // two teams of warps take alternate stages
+    constexpr int wpg = kProducerWarps / G;        // warps per team
+    const int grp = warp / wpg, wig = warp % wpg;
+    constexpr int RPW = kTileRows / wpg;           // rows of each stage this warp gathers
+    constexpr int RPL = RPW * LPR / 32;            // consecutive rows per lane (LPR lanes share a row)
     if (p.w_resident && tid == 0) {
       mbar_arrive_expect_tx(smem_u32(&s_w_full), (uint32_t)(p.kv * p.w_bytes));
       for (int k = 0; k < p.kv; ++k)   // one bulk copy per offset keeps each transfer small
@@ -200,112 +209,141 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
                  (uint32_t)p.w_bytes, smem_u32(&s_w_full));
     }
     const uint8_t* rows = (const uint8_t*)p.rows;
-    // warp w owns tile rows [32w, 32w+32); its lane l loads and parks the table entries of row 32w+l
-    int* tbl = s_tbl + warp * kRowsPerWarp + lane;   // entry of (offset k, row 32w + l) at tbl[k*256]
-    int tmp0[kTcMaxKV];
-    auto load_table = [&](int tile) {
-      const int64_t r0 = (int64_t)tile * kTileRows + warp * kRowsPerWarp + lane;
+    // Neighbour-table entries this warp needs for ONE TILE: the offsets of the stages it owns in that tile
+    // times its RPW rows, [owned stage][GK][RPW], private to the warp (at most 1024 entries: the launcher
+    // checks).  They are loaded a whole tile ahead into registers (coalesced; the table streams from HBM, and
+    // a load issued only a stage ahead sits behind the stage's copies) and parked at the tile boundary.
+    constexpr int kMaxEnt = 32;                    // registers per lane
+    constexpr int eps = GK * RPW;                  // entries per owned stage
+    int* tbl = s_tbl + warp * (kMaxEnt * 32);
+    int ent[kMaxEnt];
+    const unsigned n_rows_u = (unsigned)p.n_rows;
+    uint32_t bad = 0u;
+    const int total = my_tiles * groups;           // flat stage count of this CTA
+    auto first_owned = [&](int ti) {               // first flat stage >= ti * groups that this group owns
+      const int base = ti * groups;
+      int d = (grp - base) % G;
+      if (d < 0) d += G;
+      return base + d;
+    };
+    auto load_tile = [&](int ti) {
+      const int f0 = first_owned(ti);
+      const int f_end = (ti + 1) * groups;
+      const int64_t r0 = ((int64_t)blockIdx.x + (int64_t)ti * gridDim.x) * kTileRows + wig * RPW;
 #pragma unroll
-      for (int k = 0; k < kTcMaxKV; ++k) {
-        if (k < p.kv) {
-          const int64_t base = (int64_t)(p.flip_k ? p.kv - 1 - k : k) * p.n_out;
-          tmp0[k] = r0 < p.n_out ? __ldg(p.nbr + base + r0) : -1;
-        }
+      for (int e = 0; e < kMaxEnt; ++e) {
+        const int idx = e * 32 + lane;
+        const int f = f0 + (idx / eps) * G;
+        const int rem = idx % eps;
+        const int k = (f - ti * groups) * GK + rem / RPW;
+        const int64_t r = r0 + (rem & (RPW - 1));
+        // plain loads with no dependent work here: all 32 stay in flight; they are checked when parked
+        ent[e] = (ti < my_tiles && f < f_end && k < p.kv && r < p.n_out)
+                     ? __ldg(p.nbr + (int64_t)(p.flip_k ? p.kv - 1 - k : k) * p.n_out + r) : -1;
       }
     };
-    auto park_table = [&]() {
+    auto park_tile = [&]() {
       __syncwarp();   // every lane has finished reading the previous tile's entries
 #pragma unroll
-      for (int k = 0; k < kTcMaxKV; ++k)
-        if (k < p.kv) tbl[k * kTileRows] = tmp0[k];
+      for (int e = 0; e < kMaxEnt; ++e) {
+        int v = ent[e];
+        if ((unsigned)v >= n_rows_u) {             // -1 (absent) or an id out of range
+          bad |= (uint32_t)(v + 1);                // non-zero only for an id that is neither -1 nor valid
+          v = -1;
+        }
+        tbl[e * 32 + lane] = v;
+      }
       __syncwarp();
     };
-    load_table((int)blockIdx.x);
-    park_table();
-
-    // One gather instruction covers a few whole rows: LPR lanes copy the chunks of one row (contiguous in
-    // global memory, so a row costs one cache-line look-up instead of one per lane) and 32/LPR rows share
-    // the instruction.  A lane serves LPR consecutive rows of its warp's 32, so its table entries are
-    // adjacent in shared memory and come in with one or two vector loads ahead of the copies.
     const int l_chunk = lane % LPR;
-    const int l_row0 = (lane / LPR) * LPR;        // first of this lane's rows inside the warp's 32
-    const uint32_t lane_dst = (uint32_t)l_chunk * kRowsLbo + (uint32_t)(warp * kRowsPerWarp + l_row0) * 16u;
-    const int* tbl_row = s_tbl + warp * kRowsPerWarp + l_row0;
+    const int l_row0 = (lane / LPR) * RPL;         // first of this lane's rows inside the warp's RPW
+    const uint32_t lane_dst = (uint32_t)l_chunk * kRowsLbo + (uint32_t)(wig * RPW + l_row0) * 16u;
     const uint8_t* rows_c = rows + l_chunk * 16;
-    const unsigned n_rows_u = (unsigned)p.n_rows;
     const uint32_t row_bytes = (uint32_t)KC * 16u;
     const uint32_t stage0_u = smem_u32(stage0);
     const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
 
     SPH_PROF_BEGIN();
-    int s = 0;
-    uint32_t par = 1u;                            // parity to wait for on the empty barriers
-    uint32_t bad = 0u;
-    bool dead = false;
-    const int batch = S >= 5 ? 3 : S >= 4 ? 2 : 1;   // stages acquired per poll (costs batch - 1 stages of run-ahead)
+    int s = grp % S;                                // slot of flat stage f is f % S
+    uint32_t par = ((uint32_t)(grp / S) & 1u) ^ 1u; // parity to wait for on the slot's empty barrier
+    int ti = 0;                                     // tile of the current stage
+    int tile_end = groups;                          // first flat stage of the next tile
+    int own_j = 0;                                  // index of the current stage among this tile's owned stages
+    const int batch = S >= 5 ? 2 : 1;               // owned stages acquired per poll (costs two slots of run-ahead)
     int credits = 0;
-    for (int ti = 0; ti < my_tiles && !dead; ++ti) {
-      const bool has_next = ti + 1 < my_tiles;
-      if (has_next) load_table((int)blockIdx.x + (ti + 1) * (int)gridDim.x);
-      const int* trow = tbl_row;
-      for (int k0 = 0; k0 < p.kv; k0 += GK) {
-        // One lane polls (hundreds of threads polling one mbarrier serialise on it), and only every `batch`
-        // stages: an mbarrier operation costs ~200 cycles of the polling thread, and the MMA thread releases the
-        // slots in order, so "the slot `batch - 1` stages ahead is free" implies the ones before it are too.
-        if (credits == 0) {
-          bool ok_w = true;
-          SPH_PROF_T0();
-          if (lane == 0) {
-            int sa = s + batch - 1;
-            uint32_t pa = par;
-            if (sa >= S) { sa -= S; pa ^= 1u; }
-            ok_w = mbar_wait(empty0 + 8u * sa, pa, abort_flag);
-          }
-          SPH_PROF_ADD(1);
-          if (__any_sync(0xffffffffu, !ok_w)) { dead = true; break; }   // also orders the other lanes behind the poll
-          credits = batch;
+    load_tile(0);
+    park_tile();
+    load_tile(1);
+    for (int f = grp; f < total; f += G) {
+      while (f >= tile_end) {                       // entered the next tile: its entries are in registers
+        park_tile();
+        ++ti;
+        tile_end += groups;
+        own_j = 0;
+        load_tile(ti + 1);
+      }
+      // One lane polls (hundreds of threads polling one mbarrier serialise on it), and only every `batch` owned
+      // stages: an mbarrier operation costs ~200 cycles of the polling thread, and the MMA thread releases the
+      // slots in order, so "the slot of my stage after next is free" implies the slot of this one is too.
+      if (credits == 0) {
+        bool ok_w = true;
+        SPH_PROF_T0();
+        if (lane == 0) {
+          int sa = s + (batch - 1) * G;
+          uint32_t pa = par;
+          if (sa >= S) { sa -= S; pa ^= 1u; }
+          ok_w = mbar_wait(empty0 + 8u * sa, pa, abort_flag);
         }
-        --credits;
-        const uint32_t stage = stage0_u + (uint32_t)(s * stage_bytes);
-        if (!p.w_resident && tid == 0) {
-          const uint32_t bytes = (uint32_t)(min(GK, p.kv - k0) * p.w_bytes);
-          mbar_arrive_expect_tx(full0 + 8u * s, bytes);
-          bulk_g2s(stage + GK * X_BYTES, (const uint8_t*)p.packed + (size_t)k0 * p.w_bytes, bytes, full0 + 8u * s);
-        }
+        SPH_PROF_ADD(1);
+        if (__any_sync(0xffffffffu, !ok_w)) break;   // also orders the other lanes behind the poll
+        credits = batch;
+      }
+      --credits;
+      SPH_PROF_T0();
+      const uint32_t stage = stage0_u + (uint32_t)(s * stage_bytes);
+      const int k0 = (f - (tile_end - groups)) * GK;
+      if (!p.w_resident && wig == 0 && lane == 0) {
+        const uint32_t bytes = (uint32_t)(min(GK, p.kv - k0) * p.w_bytes);
+        mbar_arrive_expect_tx(full0 + 8u * s, bytes);
+        bulk_g2s(stage + GK * X_BYTES, (const uint8_t*)p.packed + (size_t)k0 * p.w_bytes, bytes, full0 + 8u * s);
+      }
 #pragma unroll
-        for (int g = 0; g < GK; ++g) {
-          if (GK == 1 || k0 + g < p.kv) {
+      for (int g = 0; g < GK; ++g) {
+        if (GK == 1 || k0 + g < p.kv) {
+          const int* trow = tbl + own_j * eps + g * RPW + l_row0;
+          const uint32_t dst0 = stage + (uint32_t)g * X_BYTES + lane_dst;
+#pragma unroll
+          for (int j0 = 0; j0 < RPL; j0 += LPR) {
             int r[LPR];
             if (LPR == 8) {
-              const int4 a = *(const int4*)trow, b = *(const int4*)(trow + 4);
+              const int4 a = *(const int4*)(trow + j0), b = *(const int4*)(trow + j0 + 4);
               r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
               r[4 % LPR] = b.x; r[5 % LPR] = b.y; r[6 % LPR] = b.z; r[7 % LPR] = b.w;
             } else if (LPR == 4) {
-              const int4 a = *(const int4*)trow;
+              const int4 a = *(const int4*)(trow + j0);
               r[0] = a.x; r[1] = a.y; r[2 % LPR] = a.z; r[3 % LPR] = a.w;
             } else {
-              const int2 a = *(const int2*)trow;
+              const int2 a = *(const int2*)(trow + j0);
               r[0] = a.x; r[1] = a.y;
             }
-            const uint32_t dst0 = stage + (uint32_t)g * X_BYTES + lane_dst;
 #pragma unroll
             for (int j = 0; j < LPR; ++j) {
-              const bool present = (unsigned)r[j] < n_rows_u;     // false for -1 (absent) and for ids out of range
-              bad |= (uint32_t)(r[j] + 1) & (present ? 0u : ~0u);  // non-zero only for an id that is neither -1 nor valid
+              const bool present = r[j] >= 0;
               const uint8_t* src = rows_c + (size_t)(present ? (uint32_t)r[j] : 0u) * row_bytes;
               const uint32_t sz = present ? 16u : 0u;
               // .ca: the three depth offsets of one (kh,kw) read nearly the same input rows a stage or two
               // apart, and the slice of L1 that the shared-memory carve-out leaves catches most of the repeats
-              cp_async_16_ca(dst0 + (uint32_t)j * 16u, src, sz);
-              if (PASSES == 2) cp_async_16_ca(dst0 + (uint32_t)j * 16u + 8u * kRowsLbo, src + 128, sz);
+              cp_async_16_ca(dst0 + (uint32_t)(j0 + j) * 16u, src, sz);
+              if (PASSES == 2) cp_async_16_ca(dst0 + (uint32_t)(j0 + j) * 16u + 8u * kRowsLbo, src + 128, sz);
             }
-            trow += kTileRows;
           }
         }
-        cp_async_arrive_noinc(full0 + 8u * s);
-        if (++s == S) { s = 0; par ^= 1u; }
       }
-      if (has_next && !dead) park_table();
+      SPH_PROF_ADD(2);
+      cp_async_arrive_noinc(full0 + 8u * s);
+      ++own_j;
+      s += G;
+      if (s >= S) { s -= S; par ^= 1u; }
     }
     SPH_PROF_END(0, tid == 0);
     cp_async_wait_all();
@@ -460,7 +498,7 @@ int padded_m(int N) { return N <= 64 ? 64 : 128; }
 // Fills the layout fields of p; false when two stages do not fit.
 bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   int off = 0;
-  p->tbl_off = off; off += kv * kTileRows * (int)sizeof(int);
+  p->tbl_off = off; off += kProducerWarps * 32 * 32 * (int)sizeof(int);   // 32 entries per lane and tile
   p->stg_off = off; off += kSubRows * p->N * p->out_esize;
   off = (off + 1023) & ~1023;
   p->w_off = off;
@@ -482,6 +520,9 @@ bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   const char* st_env = getenv("SPH_TC_STAGES");
   if (st_env && atoi(st_env) >= 2 && atoi(st_env) <= stages) stages = atoi(st_env);
   p->stages = stages;
+  const int gpt = (kv + gk - 1) / gk;               // stages per tile
+  if (((gpt + 1) / 2) * gk * 64 > 32 * 32) return false;   // 32 table entries per lane and tile
+  p->groups = 2;
   *smem_bytes = off + stages * stage_bytes + 1024;
   return true;
 }
