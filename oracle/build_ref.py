@@ -7,6 +7,9 @@ only copy on this machine is a 4.x tree whose MmaPipelined calls `iterator.clear
 puts a temporary copy of include/sphconv/iterator.cu.h with that one method taking the flag on the include path
 (the temporary copy is deleted afterwards; nothing of the reference is stored in this repository).
 
+A second, CPU-only module is built from the reference's host voxeliser (src/utils/all.cpp + include/point2voxel.h,
+pybind11, g++): oracle/_ref/sphconv_utils*.so.  It runs without a GPU and pins oracle/voxelize_np.py.
+
     python -m oracle.build_ref            # builds if the reference tree is present, else does nothing
 """
 import glob
@@ -111,6 +114,47 @@ def build_if_possible():
         return None
 
 
+def utils_lib_path():
+    hits = glob.glob(os.path.join(OUT, "sphconv_utils*.so"))
+    return hits[0] if hits else None
+
+
+def build_utils():
+    """The reference's host voxeliser (pybind11 module `sphconv_utils`), compiled from its own two files."""
+    import pybind11
+    os.makedirs(OUT, exist_ok=True)
+    target = os.path.join(OUT, "sphconv_utils" + sysconfig.get_config_var("EXT_SUFFIX"))
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-shared", "-fPIC", "-w",
+           "-I" + os.path.join(REFERENCE_ROOT, "include"), "-I" + pybind11.get_include(),
+           "-I" + sysconfig.get_paths()["include"], os.path.join(REFERENCE_ROOT, "src/utils/all.cpp"), "-o", target]
+    subprocess.check_call(cmd)
+    return target
+
+
+def build_utils_if_possible():
+    if utils_lib_path() is not None:
+        return utils_lib_path()
+    if not os.path.exists(os.path.join(REFERENCE_ROOT, "src/utils/all.cpp")):
+        return None
+    try:
+        return build_utils()
+    except Exception as e:
+        sys.stderr.write("[build_ref] host voxeliser not built: %s\n" % e)
+        return None
+
+
+def load_utils():
+    """Import the reference's host voxeliser module (CPU only) or return None."""
+    path = utils_lib_path()
+    if path is None:
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("sphconv_utils", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def load():
     """Import the built module (needs CUDA at call time, not at import time) or return None."""
     path = lib_path()
@@ -126,3 +170,4 @@ def load():
 
 if __name__ == "__main__":
     print(build_if_possible())
+    print(build_utils_if_possible())

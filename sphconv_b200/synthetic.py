@@ -121,3 +121,22 @@ def make_random_occupancy(rng, B, shape, density, sort_columns=True):
             rng.shuffle(seg)
             start += c
     return z_idx, z_ptr
+
+
+def make_point_cloud(rng, n_points, sph_range=(6.0, -45.0, 87.5, 70.4, 45.0, 100.0), margin=0.04, degenerate=3):
+    """Seeded stand-in for one LiDAR sweep: float32 [n_points, 4] = (x, y, z, intensity).
+
+    Directions are uniform over the angular window of `sph_range` = (r0, phi0, theta0, r1, phi1, theta1) in
+    degrees, widened by `margin` on every side so that some points fall outside the grid, ranges are log-normal
+    (most returns near), and the points come in azimuth order like a spinning sensor's.  A few degenerate points
+    (the origin, points on the z axis: undefined azimuth) exercise the not-a-number path of the transforms."""
+    r0, p0, t0, r1, p1, t1 = [float(v) for v in sph_range]
+    n = int(n_points)
+    phi = np.radians(np.sort(rng.uniform(p0 - margin * (p1 - p0), p1 + margin * (p1 - p0), n)))
+    theta = np.radians(rng.uniform(t0 - margin * (t1 - t0), t1 + margin * (t1 - t0), n))
+    r = np.exp(rng.normal(math.log(3.0 * r0), 0.7, n)).clip(0.5 * r0, 1.1 * r1)
+    pts = np.stack([r * np.sin(theta) * np.cos(phi), r * np.sin(theta) * np.sin(phi), r * np.cos(theta),
+                    rng.uniform(0.0, 1.0, n)], 1).astype(np.float32)
+    for j in range(min(int(degenerate), n)):
+        pts[(j * 7919) % n, :3] = (0.0, 0.0, 0.0 if j == 0 else float(j))
+    return pts
