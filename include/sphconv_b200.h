@@ -205,6 +205,51 @@ int sph_to_dense(void* d_rows, int32_t row_bytes, int64_t nnz, const int32_t* d_
 int sph_epilogue_backward(const void* d_dout, const void* d_out, int dtype, int64_t n, int32_t channels, int relu,
                           void* d_dpre, float* d_dbias, void* stream);
 
+/* ---- points -> range-voxel tensor (the step in front of the path; the reference does it on the host) -------------
+ * Replaces include/point2voxel.h:411-511 (points_to_voxel_3d) with its driver sphconv/utils/voxelize.py:122-219, the
+ * transforms of sphconv/utils/coord_transform.py:8-127, the mean of sphconv/vfe.py:223-228 and the init_tensor call
+ * behind them, for a batch of scans at once.
+ *
+ * sph_voxel_transform   d_points float [n, point_stride] (x, y, z, intensity, ...) -> d_sys_points float [n,4] =
+ *                       (first, second, third system coordinate, intensity), 16-byte aligned.  `system`:
+ *                       0 spherical (r, phi, theta)  1 l-spherical (log r, ...)  2 cylinder (d, phi, z)
+ *                       3 l-cylinder  4 hybrid (d, phi, theta)  5 l-hybrid.
+ * sph_voxel_grid        cells[i] / range[i], range[3+i]: cell count and low / high bound of system coordinate i
+ *                       (angles in radians, logarithms taken for the l- systems: what the reference's transform
+ *                       functions return as the system range); max_points kept per voxel (1..64), max_voxels per
+ *                       scan, append_mode 0 point features, 1 point features + system coordinates, 2 system
+ *                       coordinates + intensity (point2voxel.h:478-503).
+ * The tensor has columns (b, c0, c1) = cells of the third and second coordinate and depth c2 = cell of the first:
+ * z_ptr is [B, cells[2], cells[1]], z_idx < cells[0] (init_tensor reads coordinate rows this way, tensor.cu:30-33).
+ * Points of scan b are rows d_scan_ptr[b] .. d_scan_ptr[b+1]-1 (int32 [B+1], [0] = 0, [B] = n_points); their order is
+ * the order of the reference's walk: a voxel keeps its first max_points points, and a scan that would open more than
+ * max_voxels voxels loses every point from the one that would open voxel max_voxels + 1.
+ *
+ * sph_voxelize_count    fills d_z_ptr and the scratch, writes the row count to *h_nnz (synchronises the stream).
+ * sph_voxelize_fill     d_feature float [nnz, sph_voxel_feature_count(point_stride, append_mode)] = mean of the kept
+ *                       points; d_z_idx int32 [nnz]; optional d_coordinates int32 [nnz,4] = (b, c0, c1, c2), 16-byte
+ *                       aligned, and d_num_points int32 [nnz] (kept points per voxel).  Rows are in range-voxel order
+ *                       (ascending b, c0, c1, c2), not in the reference's first-come order. */
+typedef struct sph_voxel_grid {
+  int32_t B;
+  int32_t cells[3];
+  float range[6];
+  int32_t max_points;
+  int32_t max_voxels;
+  int32_t append_mode;
+} sph_voxel_grid;
+
+int sph_voxel_transform(const float* d_points, int32_t point_stride, int64_t n_points, int system,
+                        float* d_sys_points, void* stream);
+int sph_voxel_feature_count(int32_t point_stride, int append_mode);
+int64_t sph_voxelize_scratch_bytes(const sph_voxel_grid* grid, int64_t n_points);
+int sph_voxelize_count(const float* d_sys_points, const int32_t* d_scan_ptr, int64_t n_points,
+                       const sph_voxel_grid* grid, void* d_scratch, int32_t* d_z_ptr, int32_t* h_nnz, void* stream);
+int sph_voxelize_fill(const float* d_points, int32_t point_stride, const float* d_sys_points,
+                      const int32_t* d_scan_ptr, int64_t n_points, const sph_voxel_grid* grid, const void* d_scratch,
+                      int64_t nnz, float* d_feature, int32_t* d_z_idx, int32_t* d_coordinates, int32_t* d_num_points,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -10,6 +10,7 @@ from .tensor import SparseConvTensor
 from .sphconv_cuda import config
 from ._capi import check_status
 from .pipeline import ScanPipeline
+from .voxelize import VoxelGenerator
 
-__all__ = ["ScanPipeline", "Conv3d", "SparseConv3d", "SubMConv3d", "Sequential", "SparseSequential", "SphModule",
+__all__ = ["ScanPipeline", "VoxelGenerator", "Conv3d", "SparseConv3d", "SubMConv3d", "Sequential", "SparseSequential", "SphModule",
            "SparseConvTensor", "config", "check_status"]

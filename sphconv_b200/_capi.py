@@ -30,6 +30,12 @@ class Geom(ctypes.Structure):
                 ("stride", i32 * 3), ("padding", i32 * 3), ("tile", i32 * 2)]
 
 
+class VoxelGrid(ctypes.Structure):
+    """struct sph_voxel_grid"""
+    _fields_ = [("B", i32), ("cells", i32 * 3), ("range", ctypes.c_float * 6), ("max_points", i32),
+                ("max_voxels", i32), ("append_mode", i32)]
+
+
 # name -> (restype, argtypes); exactly the symbols include/sphconv_b200.h declares
 SIGNATURES = {
     "sph_last_error": (ctypes.c_char_p, []),
@@ -56,6 +62,11 @@ SIGNATURES = {
     "sph_permute_rows": (cint, [vp, i32, i64, vp, cint, vp, vp]),
     "sph_to_dense": (cint, [vp, i32, i64, vp, vp, i32, c_i32p, vp, cint, vp, vp]),
     "sph_epilogue_backward": (cint, [vp, vp, cint, i64, i32, cint, vp, vp, vp]),
+    "sph_voxel_transform": (cint, [vp, i32, i64, cint, vp, vp]),
+    "sph_voxel_feature_count": (cint, [i32, cint]),
+    "sph_voxelize_scratch_bytes": (i64, [ctypes.POINTER(VoxelGrid), i64]),
+    "sph_voxelize_count": (cint, [vp, vp, i64, ctypes.POINTER(VoxelGrid), vp, vp, c_i32p, vp]),
+    "sph_voxelize_fill": (cint, [vp, i32, vp, vp, i64, ctypes.POINTER(VoxelGrid), vp, i64, vp, vp, vp, vp, vp]),
 }
 
 _lib = None
