@@ -120,6 +120,72 @@ def cpu_dense_scan(cfg, scan_id, threads, w_div=1):
     return dt, float(y.abs().sum())
 
 
+def voxelize_section(cfg, B, dev, with_cpu):
+    """Not part of the timed step: the GPU voxeliser (raw points -> range-voxel tensor) on B synthetic sweeps of
+    120k points in the configuration's grid, timed with CUDA events, beside the reference's host voxeliser
+    (its compiled module when oracle/_ref holds it, else the numpy restatement) on one sweep."""
+    from sphconv_b200 import VoxelGenerator, _capi
+    cart, sph = [6, -40, -3, 70.4, 40, 1], [6, -45, 87.5, 70.4, 45, 100]       # sphconv/datagen.py:84-85
+    n_pts = 120000
+    H, W, D = cfg["shape"]
+    grid = [D, W, H]
+    rng = np.random.default_rng(4242)
+    scans = [synthetic.make_point_cloud(rng, n_pts, sph) for _ in range(B)]
+    pts = torch.as_tensor(np.concatenate(scans, 0), device=dev)
+    scan_ptr = torch.as_tensor(np.arange(B + 1, dtype=np.int32) * n_pts)
+    gen = VoxelGenerator(cart, sph, 2, 200000, grid, "spherical")
+    lib = _capi.lib()
+    for _ in range(3):
+        r = gen.generate(pts, scan_ptr, with_coordinates=False)
+    torch.cuda.synchronize()
+    reps = 10
+    l0 = lib.sph_kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        r = gen.generate(pts, scan_ptr, with_coordinates=False)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    launches = (lib.sph_kernel_launches() - l0) // reps
+    voxels = int(r["voxel_num"])
+    alg_bytes = 16.0 * B * n_pts + 20.0 * voxels + 4.0 * B * H * W     # points in, feature + z_idx out, z_ptr out
+    out = {"ms_per_batch": round(ms, 4), "scans": B, "points": B * n_pts, "voxels": voxels,
+           "scans_per_s": round(B / (ms * 1e-3), 1), "kernel_launches": int(launches),
+           "algorithmic_gbs": round(alg_bytes / (ms * 1e-3) / 1e9, 1),
+           "what": "transform + cells + first-2-points mean + z_ptr/z_idx, device resident points, includes the "
+                   "row-count read-back"}
+    if with_cpu:
+        from oracle import build_ref, voxelize_np
+        utils = build_ref.load_utils()
+        p0 = scans[0]
+        rng6 = voxelize_np.system_range(cart, sph, "spherical")
+        t0 = time.time()
+        with np.errstate(all="ignore"):
+            sys_pts = voxelize_np.system_points(p0, "spherical")
+        if utils is not None:
+            mv = 200000
+            voxels_a = np.zeros((mv, 2, 4), np.float32)
+            mask_a = np.zeros((mv, 2), np.float32)
+            coors_a = np.zeros((mv, 3), np.int32)
+            num_a = np.zeros((mv,), np.int32)
+            lookup = np.full(tuple(grid[::-1]), -1, np.int32)
+            t0 = time.time()
+            with np.errstate(all="ignore"):
+                sys_pts = voxelize_np.system_points(p0, "spherical")
+            nv = utils.points_to_voxel_3d(p0, sys_pts, voxels_a, mask_a, coors_a, num_a, lookup, rng6, grid, 2, mv, 0)
+            mean = voxels_a[:nv].sum(1) / num_a[:nv, None]
+            kind = "reference"
+        else:
+            rr = voxelize_np.points_to_voxel(p0, sys_pts, rng6, grid, 2, 200000)
+            mean = voxelize_np.simple_voxel(rr["voxels"], rr["num_points_per_voxel"])
+            kind = "port"
+        dt = time.time() - t0
+        out["cpu"] = {"scans_per_s": round(1.0 / dt, 2), "kind": kind, "cores": 1,
+                      "sample": "one sweep of %d points: transform, point2voxel walk, mean (no init_tensor)" % n_pts}
+    return out
+
+
 def run_reference(args):
     """Reference arm: the path's CPU form on the host cores (the reference has no CPU implementation of its
     CUDA kernels; its tests check them against dense torch conv3d, which is what is timed here)."""
@@ -403,6 +469,13 @@ def main():
                "sample": "%s of one %s scan through all 8 layers (forward) as dense fp32 conv3d on the densified grid, "
                          "mean of 2" % ("a 1/%d azimuth strip" % w_div if w_div > 1 else "the whole", args.workload)}
 
+    vox = None
+    if world == 1:
+        try:
+            vox = voxelize_section(cfg, B, dev, not args.no_cpu_baseline)
+        except Exception as e:          # an extra: never takes the bench line down
+            vox = {"error": str(e)[:200]}
+
     h2d, d2h = copy_bytes["h2d"], copy_bytes["d2h"]
     line = {
         "metric": "backbone scans/sec", "value": round(value, 2), "unit": "scans/s", "n_gpus": world,
@@ -423,6 +496,7 @@ def main():
         "roofline": roofline,
         "cpu_baseline": cpu,
         "clocks": clocks,
+        "voxelize": vox,
         "layers": layer_rows,
     }
     print(json.dumps(line), flush=True)

@@ -122,3 +122,33 @@ def test_tensor_feeds_the_encoder():
     conv = SubMConv3d(4, 16, 3, bias=False).to(DEV)
     out = conv(t)
     assert out.feature.shape == (t.feature.shape[0], 16) and torch.isfinite(out.feature).all()
+
+
+def test_against_the_reference_module():
+    """The reference's own compiled host voxeliser (oracle/_ref/sphconv_utils, when it was built) walks the system
+    coordinates the GPU computed; its voxel list, reordered to range-voxel rows, must equal the GPU's."""
+    from oracle import build_ref
+    utils = build_ref.load_utils()
+    if utils is None:
+        pytest.skip("oracle/_ref/sphconv_utils is not built")
+    rng = np.random.default_rng(21)
+    for system, grid, mp, mv in [("spherical", [256, 512, 64], 2, 24000), ("l-hybrid", [40, 60, 9], 2, 800)]:
+        pts, scan_ptr = _scans(rng, [40000])
+        gen = VoxelGenerator(CART_RANGE, SPH_RANGE, mp, mv, grid, system)
+        pts_d = torch.as_tensor(pts, device=DEV)
+        sys_d = gen.transform(pts_d)
+        r = gen.generate(pts_d, torch.as_tensor(scan_ptr), system_points=sys_d)
+        voxels = np.zeros((mv, mp, 4), np.float32)
+        mask = np.zeros((mv, mp), np.float32)
+        coors = np.zeros((mv, 3), np.int32)
+        num = np.zeros((mv,), np.int32)
+        lookup = np.full(tuple(grid[::-1]), -1, np.int32)
+        nv = utils.points_to_voxel_3d(pts, sys_d.cpu().numpy(), voxels, mask, coors, num, lookup, gen.system_range,
+                                      grid, mp, mv, 0)
+        assert nv == r["voxel_num"]
+        mean = voxels[:nv].sum(1) / num[:nv, None].astype(np.float32)
+        key = (coors[:nv, 0].astype(np.int64) * grid[1] + coors[:nv, 1]) * grid[0] + coors[:nv, 2]
+        order = np.argsort(key)
+        np.testing.assert_array_equal(r["coordinates"].cpu().numpy()[:, 1:], coors[:nv][order])
+        np.testing.assert_array_equal(r["num_points_per_voxel"].cpu().numpy(), num[:nv][order])
+        np.testing.assert_array_equal(r["feature"].cpu().numpy(), mean[order])
