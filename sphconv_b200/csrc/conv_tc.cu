@@ -12,8 +12,9 @@
 //               zero-filled without touching memory);
 //   D         = fp32 / int32 accumulator in TMEM, lane = output channel, column = output row.
 // A CTA owns 256 consecutive output rows at a time and is persistent over such tiles.  After the last
-// offset four epilogue warps read the accumulator back, apply scale/bias/ReLU, transpose through shared
-// memory and store whole rows.  No scatter, no atomics, every output row is written exactly once
+// offset four epilogue warps read the accumulator back, apply scale/bias/ReLU and store from registers (the lanes
+// of a warp hold consecutive channels of one row: each store instruction writes whole sectors of that row).
+// No scatter, no atomics, every output row is written exactly once
 // (the reference does a read-modify-write of the output per 8 pairs, include/sphconv/iterator.cu.h:1467-1625,
 // driven by the per-tile loop of include/sphconv/rule_conv_kernel.cu.h:91-153).
 //
@@ -46,7 +47,7 @@ constexpr int kProducerWarps = SPH_TC_PRODUCER_WARPS;    // gather warps
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kTcThreads = (kProducerWarps + 1 + 4) * 32;
-constexpr int kSubRows = 64;        // rows transposed through shared memory at a time in the epilogue
+constexpr int kSubRows = 64;        // accumulator columns (output rows) an epilogue thread reads back at a time
 constexpr int kMaxStages = 8;
 constexpr int kSmemTotal = 227 * 1024 - 2048;   // dynamic shared memory available next to the static part
 // Byte distance between K-adjacent core matrices of the gathered-row tile.  The extra 16 bytes skew the
@@ -76,38 +77,50 @@ struct TcParams {
   int out_dtype, out_esize;
   int* status;
   int num_tiles;
-  int tbl_off, stg_off, w_off, stage_off;   // dynamic shared memory layout (byte offsets)
+  int tbl_off, w_off, stage_off;   // dynamic shared memory layout (byte offsets)
 };
 
-// 16 accumulator values of one output channel (16 consecutive output rows) -> the transpose buffer.
-// The dtype switch sits outside the element loop; `dst` points at (row 0 of the 16, this channel).
-template <bool I8>
-__device__ __forceinline__ void stage_store16(uint8_t* dst, int row_pitch, int out_dtype, const uint32_t (&raw)[16],
-                                              float sc, float bi, int relu) {
-  float v[16];
+// 64 accumulator values of one output channel (64 consecutive output rows) -> the output, one element per row.
+// The lanes of a warp hold consecutive channels, so every store instruction writes one contiguous piece of a row
+// (16 or 32 channels: whole 32-byte sectors for the 16- and 32-bit types).  `dst` points at (row 0 of the 64, this
+// channel); rows >= n_valid do not exist.  The dtype switch sits outside the element loop.
+template <bool I8, typename OutT, typename Cvt>
+__device__ __forceinline__ void store_rows64(uint8_t* dst, int row_pitch, const uint32_t (&raw)[64], float sc, float bi,
+                                             int relu, int n_valid, Cvt cvt) {
+  if (n_valid >= 64) {
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    float x = I8 ? (float)(int)raw[j] : __uint_as_float(raw[j]);
-    x = fmaf(x, sc, bi);
-    v[j] = relu ? fmaxf(x, 0.f) : x;
+    for (int j = 0; j < 64; ++j) {
+      float x = I8 ? (float)(int)raw[j] : __uint_as_float(raw[j]);
+      x = fmaf(x, sc, bi);
+      *(OutT*)(dst + (size_t)j * row_pitch) = cvt(relu ? fmaxf(x, 0.f) : x);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 64; ++j) {
+      float x = I8 ? (float)(int)raw[j] : __uint_as_float(raw[j]);
+      x = fmaf(x, sc, bi);
+      if (j < n_valid) *(OutT*)(dst + (size_t)j * row_pitch) = cvt(relu ? fmaxf(x, 0.f) : x);
+    }
   }
+}
+
+template <bool I8>
+__device__ __forceinline__ void store_rows64_any(uint8_t* dst, int row_pitch, int out_dtype, const uint32_t (&raw)[64],
+                                                 float sc, float bi, int relu, int n_valid) {
   switch (out_dtype) {
     case SPH_F32:
-#pragma unroll
-      for (int j = 0; j < 16; ++j) *(float*)(dst + j * row_pitch) = v[j];
+      store_rows64<I8, float>(dst, row_pitch, raw, sc, bi, relu, n_valid, [](float v) { return v; });
       break;
     case SPH_F16:
-#pragma unroll
-      for (int j = 0; j < 16; ++j) *(__half*)(dst + j * row_pitch) = __float2half_rn(v[j]);
+      store_rows64<I8, __half>(dst, row_pitch, raw, sc, bi, relu, n_valid, [](float v) { return __float2half_rn(v); });
       break;
     case SPH_BF16:
-#pragma unroll
-      for (int j = 0; j < 16; ++j) *(__nv_bfloat16*)(dst + j * row_pitch) = __float2bfloat16_rn(v[j]);
+      store_rows64<I8, __nv_bfloat16>(dst, row_pitch, raw, sc, bi, relu, n_valid,
+                                      [](float v) { return __float2bfloat16_rn(v); });
       break;
     default:
-#pragma unroll
-      for (int j = 0; j < 16; ++j)
-        *(int8_t*)(dst + j * row_pitch) = (int8_t)(int)fminf(fmaxf(rintf(v[j]), -127.f), 127.f);
+      store_rows64<I8, int8_t>(dst, row_pitch, raw, sc, bi, relu, n_valid,
+                               [](float v) { return (int8_t)(int)fminf(fmaxf(rintf(v), -127.f), 127.f); });
   }
 }
 
@@ -129,8 +142,6 @@ __device__ long long g_tc_prof[256][12];
 #define SPH_PROF_ADD(i)
 #define SPH_PROF_END(base, pred)
 #endif
-
-__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // KC = 16-byte chunks per gathered row (2, 4, 8, 16), I8 = int8 operands.  Both are compile-time so that the
 // per-stage instruction streams of the gather warps and of the MMA thread have no loops or branches to
@@ -158,7 +169,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   const int S = p.stages;
   const int stage_bytes = GK * ((int)X_BYTES + (p.w_resident ? 0 : p.w_bytes));
   int* s_tbl = (int*)(smem + p.tbl_off);          // per producer warp: neighbour rows of its share of one stage
-  uint8_t* s_stg = smem + p.stg_off;              // [64][N] epilogue transpose buffer
   uint8_t* w_smem = smem + p.w_off;               // resident weight images (if any)
   uint8_t* stage0 = smem + p.stage_off;
   const int groups = (p.kv + GK - 1) / GK;        // stages per tile
@@ -414,13 +424,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
   } else {
     // ======================= epilogue =======================
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
-    const int et = q * 32 + lane;                 // 0..127 among the epilogue threads
     // accumulator row (= output channel) held by this thread's TMEM lane
     const int oc = p.MP == 64 ? (lane < 16 ? 16 * q + lane : -1) : 32 * q + lane;
     const bool has_oc = oc >= 0 && oc < p.N;
     const float sc = (has_oc && p.scale) ? __ldg(p.scale + oc) : 1.f;
     const float bi = (has_oc && p.bias) ? __ldg(p.bias + oc) : 0.f;
-    const int row_pitch = p.N * p.out_esize;      // bytes of one output row; the staging buffer uses the same pitch
+    const int row_pitch = p.N * p.out_esize;      // bytes of one output row
     SPH_PROF_BEGIN();
     for (int ti = 0; ti < my_tiles; ++ti) {
       const int buf = ti & 1;
@@ -434,24 +443,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams 
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTileRows);
       for (int sub = 0; sub < kTileRows / kSubRows; ++sub) {
         const int64_t row0 = tile * kTileRows + sub * kSubRows;
-        if (row0 >= p.n_out) break;               // uniform over the four warps
-        for (int c0 = 0; c0 < kSubRows; c0 += 16) {
-          uint32_t raw[16];
-          tmem_ld16(taddr + (uint32_t)(sub * kSubRows + c0), raw);
-          tmem_ld_wait();
-          if (has_oc)
-            stage_store16<I8>(s_stg + c0 * row_pitch + oc * p.out_esize, row_pitch, p.out_dtype, raw, sc, bi, p.relu);
-        }
-        epilogue_bar();
-        // the 64 rows are one contiguous range of the output: copy it out with 16-byte stores
-        const int64_t rows_here = min((int64_t)kSubRows, p.n_out - row0);
-        const int nbytes = (int)rows_here * row_pitch;
-        uint8_t* gdst = (uint8_t*)p.out + row0 * row_pitch;
-        const int nvec = nbytes & ~15;
-        for (int off = et * 16; off < nvec; off += 128 * 16)
-          *(uint4*)(gdst + off) = *(const uint4*)(s_stg + off);
-        for (int off = nvec + et; off < nbytes; off += 128) gdst[off] = s_stg[off];   // ragged last rows
-        epilogue_bar();
+        if (row0 >= p.n_out) break;               // warp-uniform
+        uint32_t raw[kSubRows];
+        tmem_ld64(taddr + (uint32_t)(sub * kSubRows), raw);
+        tmem_ld_wait();
+        // straight from registers to the output: no staging buffer, no barrier between the four warps (each
+        // writes its own channels of the 64 rows)
+        if (has_oc)
+          store_rows64_any<I8>((uint8_t*)p.out + row0 * row_pitch + oc * p.out_esize, row_pitch, p.out_dtype, raw, sc,
+                               bi, p.relu, (int)min((int64_t)kSubRows, p.n_out - row0));
       }
       tc_fence_before();
       __syncwarp();
@@ -494,12 +494,11 @@ __global__ void pack_weight_kernel(const T* __restrict__ w, int kv, int K, int N
 
 int padded_m(int N) { return N <= 64 ? 64 : 128; }
 
-// Dynamic shared-memory layout: neighbour table, epilogue transpose buffer, (resident weights), stages.
+// Dynamic shared-memory layout: neighbour table, (resident weights), stages.
 // Fills the layout fields of p; false when two stages do not fit.
 bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   int off = 0;
   p->tbl_off = off; off += kProducerWarps * 32 * 32 * (int)sizeof(int);   // 32 entries per lane and tile
-  p->stg_off = off; off += kSubRows * p->N * p->out_esize;
   off = (off + 1023) & ~1023;
   p->w_off = off;
   const int gk = p->kc == 2 ? 4 : p->kc == 4 ? 3 : 1;   // kernel offsets per stage (must match the kernel's GK)
