@@ -375,6 +375,10 @@ def main():
         torch.cuda.synchronize()
         pairs_of = dict(profiling.pair_counts)
         profiling.pair_counts = None
+        # the counting pass left its temporaries in the allocator's cache: settle it again before timing
+        for _ in range(2):
+            step_resident()
+        torch.cuda.synchronize()
 
         # ---- resident-input timing (value), with per-layer sections for the roofline
         barrier()
