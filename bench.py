@@ -225,6 +225,8 @@ def main():
     ap.add_argument("--workload", default="cfg3", choices=["cfg3", "cfg4", "cfg5"])
     ap.add_argument("--batch", type=int, default=0, help="scans per rank per step (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the measurements reported beside the metric (tables-only step, voxeliser): for profiler runs")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -391,6 +393,21 @@ def main():
         barrier()
         total_ms = max_over_ranks(sum(times))
 
+        # ---- the same step when the module path keeps only the neighbour tables (what the convolution kernels read)
+        # and skips the reference-format pair lists `rules` / `rule_size`; reported beside `value`, never as it
+        tables_ms = None
+        if not args.no_extras:
+            sphconv.config.materialize_rules = False
+            for _ in range(2):
+                step_resident()
+            barrier()
+            tables_ms = max_over_ranks(sum(timed(step_resident, args.steps)))
+            sphconv.check_status()
+            sphconv.config.materialize_rules = True
+            for _ in range(2):
+                step_resident()
+            barrier()
+
         # ---- end to end from pinned host buffers
         run_e2e(3, flush)
         barrier()
@@ -474,7 +491,7 @@ def main():
                          "mean of 2" % ("a 1/%d azimuth strip" % w_div if w_div > 1 else "the whole", args.workload)}
 
     vox = None
-    if world == 1:
+    if world == 1 and not args.no_extras:
         try:
             vox = voxelize_section(cfg, B, dev, not args.no_cpu_baseline)
         except Exception as e:          # an extra: never takes the bench line down
@@ -500,6 +517,11 @@ def main():
         "roofline": roofline,
         "cpu_baseline": cpu,
         "clocks": clocks,
+        "tables_only": None if tables_ms is None else {
+                        "value": round(scans / (tables_ms * 1e-3), 2), "unit": "scans/s",
+                        "ms_per_step": round(tables_ms / args.steps, 4),
+                        "what": "sphconv_b200.config.materialize_rules = False: the layers keep the neighbour tables "
+                                "and do not write the reference-format rules / rule_size tensors (same outputs)"},
         "voxelize": vox,
         "layers": layer_rows,
     }
