@@ -531,8 +531,8 @@ def main():
 
 
 # DRAM bytes (read + write) per output row of one launch of the dominant kernel, from the ncu capture summarised in
-# profiles/conv_gather_tc_64to64_fp16_b4_full.md (97.5 MB for 346.8 k rows); traffic grows in proportion to rows.
-TRAFFIC_BYTES_PER_OUT_ROW = {"fp16": 281.0}
+# profiles/conv_gather_tc_64to64_fp16_b4_full.md (97.9 MB for 346.8 k rows); traffic grows in proportion to rows.
+TRAFFIC_BYTES_PER_OUT_ROW = {"fp16": 282.0}
 
 if __name__ == "__main__":
     main()

@@ -49,6 +49,7 @@ constexpr int kMmaWarp = kProducerWarps;
 constexpr int kTcThreads = (kProducerWarps + 1 + 4) * 32;
 constexpr int kSubRows = 64;        // accumulator columns (output rows) an epilogue thread reads back at a time
 constexpr int kMaxStages = 8;
+constexpr int kRingStages = 4;     // pipeline slots used (see plan_smem)
 constexpr int kSmemTotal = 227 * 1024 - 2048;   // dynamic shared memory available next to the static part
 // Byte distance between K-adjacent core matrices of the gathered-row tile.  The extra 16 bytes skew the
 // chunks of one row across the shared-memory banks, so the 32 lanes of a gather instruction (a few rows x
@@ -508,8 +509,10 @@ bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   // hidden by the depth of the ring); resident wins ties because it saves the re-streaming
   int st_res = avail >= w_all ? (avail - w_all) / (gk * p->x_bytes) : 0;
   int st_str = avail / (gk * (p->x_bytes + p->w_bytes));
-  if (st_res > kMaxStages) st_res = kMaxStages;
-  if (st_str > kMaxStages) st_str = kMaxStages;
+  // Four slots are enough run-ahead for the two teams; a deeper ring measured no faster, and the shared memory it
+  // does not take stays with L1, which the gathers hit (the depth offsets of one (kh,kw) share rows).
+  if (st_res > kRingStages) st_res = kRingStages;
+  if (st_str > kRingStages) st_str = kRingStages;
   p->w_resident = (st_res >= 2 && st_res >= st_str) ? 1 : 0;
   int stages = p->w_resident ? st_res : st_str;
   if (p->w_resident) off += w_all;
