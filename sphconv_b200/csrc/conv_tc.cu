@@ -44,6 +44,9 @@ constexpr int kTileRows = 256;      // output rows per tile = UMMA N
 #define SPH_TC_PRODUCER_WARPS 8
 #endif
 constexpr int kProducerWarps = SPH_TC_PRODUCER_WARPS;    // gather warps
+#ifndef SPH_GK4
+#define SPH_GK4 3                   // kernel offsets per pipeline stage for 64-byte rows
+#endif
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kTcThreads = (kProducerWarps + 1 + 4) * 32;
@@ -150,7 +153,7 @@ __device__ long long g_tc_prof[256][12];
 // streams, not the tensor pipe or the memory system, set the pace once the data path is asynchronous.
 template <int KC, bool I8>
 __global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams p) {
-  constexpr int GK = KC == 2 ? 4 : KC == 4 ? 3 : 1;   // kernel offsets per pipeline stage
+  constexpr int GK = KC == 2 ? 4 : KC == 4 ? SPH_GK4 : 1;   // kernel offsets per pipeline stage
   constexpr int LPR = KC < 8 ? KC : 8;           // lanes per row = rows per lane
   constexpr int PASSES = KC / LPR;               // 2 only for 256-byte rows
   constexpr int NMMA = KC / 2;                   // 32 bytes of K per instruction
@@ -502,7 +505,7 @@ bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   p->tbl_off = off; off += kProducerWarps * 32 * 32 * (int)sizeof(int);   // 32 entries per lane and tile
   off = (off + 1023) & ~1023;
   p->w_off = off;
-  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? 3 : 1;   // kernel offsets per stage (must match the kernel's GK)
+  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? SPH_GK4 : 1;   // kernel offsets per stage (must match the kernel's GK)
   const int w_all = kv * p->w_bytes;
   const int avail = kSmemTotal - 1024 - off;            // 1 KB slack: the M = 64/128 instruction reads past a short image
   // resident weights or one image per stage: whichever keeps more gathered offsets in flight (memory latency is
