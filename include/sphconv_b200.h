@@ -117,6 +117,14 @@ int64_t sph_rules_strided_scratch_bytes(const sph_geom* g, int64_t nnz);
 int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
                             void* d_scratch, int32_t* d_oz_ptr, int32_t* d_out_nnz, int32_t* h_out_nnz,
                             void* stream);
+/* The same without the synchronisation: enqueues step 1 and returns in *h_count_word the address of the mapped host
+ * word the count will be written to; it may be read once work enqueued on `stream` up to this call has completed
+ * (e.g. after cudaEventSynchronize on an event recorded right after the call).  Lets a caller enqueue other work
+ * behind step 1 - the convolution of the layer before - so that the GPU is busy during the host's round trip.
+ * At most 256 such words per device are in use at a time (a ring): read the count before 255 further calls. */
+int sph_rules_strided_count_async(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* g,
+                                  void* d_scratch, int32_t* d_oz_ptr, int32_t* d_out_nnz,
+                                  const int32_t** h_count_word, void* stream);
 
 /* Strided sparse conv, step 2: output depth indices, rules and neighbour tables.
  * ref: getOzIndicesAndRulesKernel, src/sphconv/rules.cu:156-228,465-485.  Output rows are numbered in

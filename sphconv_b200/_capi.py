@@ -49,6 +49,8 @@ SIGNATURES = {
     "sph_rules_subm_static": (cint, [vp, vp, i64, ctypes.POINTER(Geom), i32, vp, vp, vp, cint, vp, vp]),
     "sph_rules_strided_scratch_bytes": (i64, [ctypes.POINTER(Geom), i64]),
     "sph_rules_strided_count": (cint, [vp, vp, i64, ctypes.POINTER(Geom), vp, vp, vp, c_i32p, vp]),
+    "sph_rules_strided_count_async": (cint, [vp, vp, i64, ctypes.POINTER(Geom), vp, vp, vp,
+                                             ctypes.POINTER(ctypes.c_void_p), vp]),
     "sph_rules_strided_fill": (cint, [vp, vp, i64, ctypes.POINTER(Geom), vp, vp, i64, i32, vp, vp, vp, vp, vp, cint,
                                       vp, vp]),
     "sph_rules_to_nbr": (cint, [vp, vp, i32, i32, i32, i64, i64, vp, vp, vp, vp]),

@@ -91,11 +91,29 @@ class Conv3d(Convolution):
         self.activation = activation
 
     def _rules(self, input: SparseConvTensor, in_shape, out_shape):
-        fn = ops.get_rules_subm if self.subm else ops.get_rules
-        oz_idx, oz_ptr, rules, rule_size = fn(input.z_idx, input.z_ptr, input.B, in_shape, out_shape,
-                                              self.kernel_size, self.stride, self.padding, self.dilation,
-                                              self.tile_size)
+        args = (input.z_idx, input.z_ptr, input.B, in_shape, out_shape, self.kernel_size, self.stride, self.padding,
+                self.dilation, self.tile_size)
+        if self.subm:
+            oz_idx, oz_ptr, rules, rule_size = ops.get_rules_subm(*args)
+        else:
+            pending = input.rule_cache.pop(("pending", id(self)), None)
+            oz_idx, oz_ptr, rules, rule_size = ops.get_rules(*args, pending=pending)
         return oz_idx, oz_ptr, rules, rule_size, get_tile_grid_shape(out_shape, self.tile_size)
+
+    def begin_rules(self, input: SparseConvTensor):
+        """Extension used by Sequential: enqueue the first step of this (strided) layer's rule generation on a tensor
+        that has the geometry this layer will see - the input of the submanifold layer in front of it - so that
+        the layer in front runs on the GPU while the host waits for the output row count.  The handle travels in
+        the tensor's rule cache, which the layers of a stack share."""
+        if self.subm or (self.indice_key is not None and input.find_rule(self.indice_key) is not None):
+            return
+        in_shape = [input.D, input.W, input.H]
+        out_shape = out_spatial(in_shape, self.kernel_size, self.stride, self.padding, self.dilation)
+        tag = self.name or "conv{}_{}".format(self.in_channels, self.weight.shape[4])
+        with profiling.section("rules:" + tag, subm=False, n_in=input.feature.shape[0]):
+            input.rule_cache[("pending", id(self))] = ops.get_rules_begin(
+                input.z_idx, input.z_ptr, input.B, in_shape, out_shape, self.kernel_size, self.stride, self.padding,
+                self.dilation, self.tile_size)
 
     def forward(self, input: SparseConvTensor):
         batch_size, in_channels = input.B, input.C

@@ -1006,14 +1006,17 @@ extern "C" int64_t sph_rules_strided_scratch_bytes(const sph_geom* s, int64_t nn
   return (int64_t)(l.mask_bytes + l.blocksum_bytes + l.colmask_bytes);
 }
 
-extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz,
-                                       const sph_geom* s, void* d_scratch, int32_t* d_oz_ptr, int32_t* d_out_nnz,
-                                       int32_t* h_out_nnz, void* stream) {
+namespace {
+
+// Launches the kernels of step 1.  With want_host_word the scan also writes the count to a word of mapped pinned
+// host memory whose address is returned (readable once the work enqueued so far has completed).
+int strided_count_impl(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz, const sph_geom* s, void* d_scratch,
+                       int32_t* d_oz_ptr, int32_t* d_out_nnz, bool want_host_word, int32_t** host_word_out,
+                       cudaStream_t st) {
   Geom g;
   int rc = make_geom(s, &g);
   if (rc != SPH_OK) return rc;
   SPH_CHECK_ARG(d_z_ptr && d_scratch && d_oz_ptr && d_out_nnz && (nnz == 0 || d_z_idx), "null argument");
-  cudaStream_t st = (cudaStream_t)stream;
   StridedScratch l = strided_layout(g, nnz);
   uint32_t* mask = (uint32_t*)d_scratch;
   int* blocksum = (int*)((char*)d_scratch + l.mask_bytes);
@@ -1035,7 +1038,7 @@ extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_
   }
   int32_t* host_word = nullptr;
   int32_t* dev_word = nullptr;
-  if (h_out_nnz) {
+  if (want_host_word) {
     rc = count_slot(&host_word, &dev_word);
     if (rc != SPH_OK) return rc;
   }
@@ -1043,10 +1046,36 @@ extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_
   SPH_LAUNCH_CHECK();
   scan_columns_kernel<<<l.nblk, kScanThreads, 0, st>>>(d_oz_ptr, l.ncols, blocksum);
   SPH_LAUNCH_CHECK();
+  if (host_word_out) *host_word_out = host_word;
+  return SPH_OK;
+}
+
+}  // namespace
+
+extern "C" int sph_rules_strided_count(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz,
+                                       const sph_geom* s, void* d_scratch, int32_t* d_oz_ptr, int32_t* d_out_nnz,
+                                       int32_t* h_out_nnz, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t* host_word = nullptr;
+  int rc = strided_count_impl(d_z_idx, d_z_ptr, nnz, s, d_scratch, d_oz_ptr, d_out_nnz, h_out_nnz != nullptr,
+                              &host_word, st);
+  if (rc != SPH_OK) return rc;
   if (h_out_nnz) {
     SPH_CUDA(cudaStreamSynchronize(st));
     *h_out_nnz = *(volatile int32_t*)host_word;
   }
+  return SPH_OK;
+}
+
+extern "C" int sph_rules_strided_count_async(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64_t nnz,
+                                             const sph_geom* s, void* d_scratch, int32_t* d_oz_ptr,
+                                             int32_t* d_out_nnz, const int32_t** h_count_word, void* stream) {
+  SPH_CHECK_ARG(h_count_word != nullptr, "null argument");
+  int32_t* host_word = nullptr;
+  int rc = strided_count_impl(d_z_idx, d_z_ptr, nnz, s, d_scratch, d_oz_ptr, d_out_nnz, true, &host_word,
+                              (cudaStream_t)stream);
+  if (rc != SPH_OK) return rc;
+  *h_count_word = host_word;
   return SPH_OK;
 }
 

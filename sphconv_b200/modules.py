@@ -63,9 +63,16 @@ class Sequential(SphModule):
         from .conv import Conv3d, SubMConv3d
         from .tensor import SparseConvTensor
         nvtx = torch.cuda.nvtx if torch.cuda.is_available() else None
-        for k, module in self._modules.items():
+        items = list(self._modules.items())
+        for pos, (k, module) in enumerate(items):
             if is_sph_module(module):
                 assert isinstance(input, SparseConvTensor)
+                if isinstance(module, Conv3d) and module.subm:
+                    # a submanifold layer keeps the geometry: the strided layer behind it can start finding its
+                    # output pattern now, and this layer's convolution covers the host's wait for the row count
+                    nxt = next((m for _, m in items[pos + 1:] if is_sph_module(m)), None)
+                    if isinstance(nxt, Conv3d) and not nxt.subm:
+                        nxt.begin_rules(input)
                 if nvtx is not None:
                     tag = "SubMConv3d" if isinstance(module, SubMConv3d) else \
                         "Conv3d" if isinstance(module, Conv3d) else "layer"

@@ -85,28 +85,69 @@ def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, s
     return [zIndices, zPtr, tables, None]
 
 
-def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
-              outSpatialShape: List[int], kernelSize: List[int], stride: List[int], padding: List[int],
-              dilation: List[int], tileSize: List[int]):
-    """ref: get_rules, src/sphconv/rules.cu:405-486.  Returns [ozIndices, ozPtr, rules, ruleSize]."""
+class PendingRules:
+    """Step 1 of a strided rule set (output sparsity pattern) that has been enqueued but whose row count has not been
+    read yet; `get_rules(..., pending=...)` completes it."""
+    __slots__ = ("z_idx", "z_ptr", "key", "geom", "scratch", "oz_ptr", "d_count", "count_word", "event")
+
+    def matches(self, zIndices, zPtr, key):
+        return self.z_idx is zIndices and self.z_ptr is zPtr and self.key == key
+
+
+def _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize):
+    return (int(batchSize),) + tuple(int(v) for seq in (spatialShape, outSpatialShape, kernelSize, stride, padding,
+                                                        tileSize) for v in seq)
+
+
+def get_rules_begin(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
+                    outSpatialShape: List[int], kernelSize: List[int], stride: List[int], padding: List[int],
+                    dilation: List[int], tileSize: List[int]) -> PendingRules:
+    """Enqueues step 1 of get_rules without waiting for the row count.  Work enqueued after this call (the
+    convolution of the previous layer, say) keeps the GPU busy while the host later waits for the count."""
     _check_common(zIndices, zPtr, dilation)
     lib = C.lib()
     dev = zIndices.device
     nnz = zIndices.shape[0]
-    g = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    p = PendingRules()
+    p.z_idx, p.z_ptr = zIndices, zPtr
+    p.key = _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    p.geom = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    scratch_bytes = C.check(lib.sph_rules_strided_scratch_bytes(ctypes.byref(p.geom), nnz))
+    p.scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=dev)
+    p.oz_ptr = torch.empty((batchSize, int(outSpatialShape[0]), int(outSpatialShape[1])), dtype=torch.int32, device=dev)
+    p.d_count = torch.empty((1,), dtype=torch.int32, device=dev)
+    word = ctypes.c_void_p(0)
+    with torch.cuda.device(dev):
+        C.check(lib.sph_rules_strided_count_async(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(p.geom),
+                                                  C.ptr(p.scratch), C.ptr(p.oz_ptr), C.ptr(p.d_count),
+                                                  ctypes.byref(word), C.stream_ptr(dev)))
+        p.event = torch.cuda.Event()
+        p.event.record(torch.cuda.current_stream(dev))
+    p.count_word = word.value
+    return p
+
+
+def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
+              outSpatialShape: List[int], kernelSize: List[int], stride: List[int], padding: List[int],
+              dilation: List[int], tileSize: List[int], pending: Optional[PendingRules] = None):
+    """ref: get_rules, src/sphconv/rules.cu:405-486.  Returns [ozIndices, ozPtr, rules, ruleSize].
+    `pending` (extension): the result of get_rules_begin on the same arguments; step 1 is then not run again."""
+    key = _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    if pending is None or not pending.matches(zIndices, zPtr, key):
+        pending = get_rules_begin(zIndices, zPtr, batchSize, spatialShape, outSpatialShape, kernelSize, stride,
+                                  padding, dilation, tileSize)
+    lib = C.lib()
+    dev = zIndices.device
+    nnz = zIndices.shape[0]
+    g = pending.geom
     kv = int(kernelSize[0]) * int(kernelSize[1]) * int(kernelSize[2])
     n_tile = C.check(lib.sph_num_tiles(ctypes.byref(g)))
-    scratch_bytes = C.check(lib.sph_rules_strided_scratch_bytes(ctypes.byref(g), nnz))
-    scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=dev)
-    oz_ptr = torch.empty((batchSize, int(outSpatialShape[0]), int(outSpatialShape[1])), dtype=torch.int32, device=dev)
-    d_count = torch.empty((1,), dtype=torch.int32, device=dev)
-    h_count = ctypes.c_int32(0)
+    scratch, oz_ptr = pending.scratch, pending.oz_ptr
     status = C.status_tensor(dev)
+    pending.event.synchronize()      # the same device -> host read the reference does at rules.cu:461
+    out_nnz = int(ctypes.c_int32.from_address(pending.count_word).value)
     with torch.cuda.device(dev):
         st = C.stream_ptr(dev)
-        C.check(lib.sph_rules_strided_count(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), C.ptr(scratch),
-                                            C.ptr(oz_ptr), C.ptr(d_count), ctypes.byref(h_count), st))
-        out_nnz = int(h_count.value)
         oz_idx = torch.empty((out_nnz,), dtype=torch.int32, device=dev)
         rules = rule_size = None
         tnm = 0

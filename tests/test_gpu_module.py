@@ -119,3 +119,55 @@ def test_fused_bias_relu_extension_matches_unfused():
     # the reference applies no bias by default (sphconv/conv.py:182-185)
     with torch.no_grad():
         assert not torch.allclose(plain(mk()).feature.float(), ref)
+
+
+def test_sequential_starts_strided_rules_ahead():
+    """Sequential enqueues the first step of a strided layer's rule generation before the submanifold layer in front
+    of it runs; outputs and rules are those of the layers called one by one."""
+    from sphconv_b200 import sphconv_cuda as ops
+    rng = np.random.default_rng(31)
+    B, shape = 2, [12, 20, 16]
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.25)
+    feat = torch.as_tensor(rng.standard_normal((z_idx.shape[0], 16)), dtype=torch.float16, device=DEV)
+    zi, zp = torch.as_tensor(z_idx, device=DEV), torch.as_tensor(z_ptr, device=DEV)
+    torch.manual_seed(3)
+    net = sphconv.Sequential(
+        sphconv.SubMConv3d(16, 16, 3, indice_key="a", name="s0"),
+        torch.nn.ReLU(),
+        sphconv.SparseConv3d(16, 32, 3, stride=2, padding=1, name="d0"),
+        sphconv.SubMConv3d(32, 32, 3, indice_key="b", name="s1"),
+        sphconv.SparseConv3d(32, 32, 3, stride=2, padding=1, name="d1"),
+    ).to(DEV).half().eval()
+    calls = []
+    real_begin = ops.get_rules_begin
+
+    def spy(*a, **k):
+        calls.append(a[0])
+        return real_begin(*a, **k)
+
+    ops.get_rules_begin = spy
+    try:
+        with torch.no_grad():
+            x = sphconv.SparseConvTensor(feat, shape, B, z_idx=zi, z_ptr=zp)
+            y = net(x)
+            assert len(calls) == 2                      # one per strided layer, none repeated by get_rules
+            assert not any(isinstance(k, tuple) for k in y.rule_cache)     # the handles were consumed
+            t = sphconv.SparseConvTensor(feat, shape, B, z_idx=zi, z_ptr=zp)
+            for m in net:
+                if isinstance(m, torch.nn.ReLU):
+                    t.feature = m(t.feature)
+                else:
+                    t = m(t)
+            assert len(calls) == 4                      # called one by one: get_rules runs both steps itself
+    finally:
+        ops.get_rules_begin = real_begin
+    assert torch.equal(y.z_idx, t.z_idx) and torch.equal(y.z_ptr, t.z_ptr) and torch.equal(y.feature, t.feature)
+    sphconv.check_status()
+    # the handle API itself: a mismatching handle is ignored, a matching one is used
+    geom = (zi, zp, B, shape, [6, 10, 8], [3, 3, 3], [2, 2, 2], [1, 1, 1], [1, 1, 1], [2, 2])
+    want = ops.get_rules(*geom)
+    pend = ops.get_rules_begin(*geom)
+    got = ops.get_rules(*geom, pending=pend)
+    other = ops.get_rules(zi.clone(), zp, *geom[2:], pending=ops.get_rules_begin(*geom))
+    for a, b, c in zip(want, got, other):
+        assert torch.equal(a, b) and torch.equal(a, c)
