@@ -137,6 +137,16 @@ int sph_rules_strided_fill(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64
                            int32_t tile_n_max, int32_t* d_oz_idx, int32_t* d_rules, int32_t* d_rule_size,
                            int32_t* d_nbr, int32_t* d_nbr_t, int fill_unused, int32_t* d_status, void* stream);
 
+/* The reference-format pair lists of a rule set from its finished neighbour table: what sph_rules_subm /
+ * sph_rules_strided_fill write into d_rules / d_rule_size, as a step of its own, so that a caller whose convolution
+ * reads only the table can call those with d_rules = NULL and run this step on another stream, beside the convolution.
+ *   d_oz_ptr   int32 [B,oH,oW] of the OUTPUT tensor (z_ptr itself for a submanifold layer)
+ *   d_nbr      int32 [KV, out_nnz]   tile_n_max, d_rules, d_rule_size, fill_unused: as for sph_rules_subm
+ * Lists come out in ascending output row per batch, whatever the order inside the columns. */
+int sph_rule_lists(const int32_t* d_oz_ptr, const sph_geom* g, int64_t out_nnz, const int32_t* d_nbr,
+                   int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int fill_unused, int32_t* d_status,
+                   void* stream);
+
 /* Neighbour tables from a reference-format rules tensor (for rules that did not come from this library).
  * ref: the consumer side of the format, include/sphconv/iterator.cu.h:147-181 (reads rules[t][k][0|1][v], v < ruleSize).
  *   d_nbr   int32 [KV, out_rows] (may be null)   d_nbr_t int32 [KV, in_rows] (may be null) */

@@ -53,6 +53,7 @@ SIGNATURES = {
                                              ctypes.POINTER(ctypes.c_void_p), vp]),
     "sph_rules_strided_fill": (cint, [vp, vp, i64, ctypes.POINTER(Geom), vp, vp, i64, i32, vp, vp, vp, vp, vp, cint,
                                       vp, vp]),
+    "sph_rule_lists": (cint, [vp, ctypes.POINTER(Geom), i64, vp, i32, vp, vp, cint, vp, vp]),
     "sph_rules_to_nbr": (cint, [vp, vp, i32, i32, i32, i64, i64, vp, vp, vp, vp]),
     "sph_packed_weight_bytes": (i64, [cint, i32, i32, i32]),
     "sph_pack_weight": (cint, [vp, cint, i32, i32, i32, vp, vp]),

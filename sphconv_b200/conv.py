@@ -93,11 +93,13 @@ class Conv3d(Convolution):
     def _rules(self, input: SparseConvTensor, in_shape, out_shape):
         args = (input.z_idx, input.z_ptr, input.B, in_shape, out_shape, self.kernel_size, self.stride, self.padding,
                 self.dilation, self.tile_size)
+        # defer_lists: the reference-format pair lists are written on a side stream while this layer's convolution,
+        # which reads the neighbour table only, runs; rule_conv orders the stream behind them again
         if self.subm:
-            oz_idx, oz_ptr, rules, rule_size = ops.get_rules_subm(*args)
+            oz_idx, oz_ptr, rules, rule_size = ops.get_rules_subm(*args, defer_lists=True)
         else:
             pending = input.rule_cache.pop(("pending", id(self)), None)
-            oz_idx, oz_ptr, rules, rule_size = ops.get_rules(*args, pending=pending)
+            oz_idx, oz_ptr, rules, rule_size = ops.get_rules(*args, pending=pending, defer_lists=True)
         return oz_idx, oz_ptr, rules, rule_size, get_tile_grid_shape(out_shape, self.tile_size)
 
     def begin_rules(self, input: SparseConvTensor):

@@ -152,7 +152,7 @@ __device__ long long g_tc_prof[256][12];
 // resolve: with two or three warps per scheduler nothing hides a lone warp's instruction latency, and those
 // streams, not the tensor pipe or the memory system, set the pace once the data path is asynchronous.
 template <int KC, bool I8>
-__global__ void __launch_bounds__(kTcThreads, 1) conv_gather_tc_kernel(TcParams p) {
+__global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
   constexpr int GK = KC == 2 ? 4 : KC == 4 ? SPH_GK4 : 1;   // kernel offsets per pipeline stage
   constexpr int LPR = KC < 8 ? KC : 8;           // lanes per row = rows per lane
   constexpr int PASSES = KC / LPR;               // 2 only for 256-byte rows

@@ -323,7 +323,7 @@ rule_lists_kernel(const int* __restrict__ out_zp, Geom g, int64_t out_nnz, int t
                   const int* __restrict__ unsorted, int* __restrict__ status) {
   __shared__ int s_rs[kListWarps][kListRanges];
   __shared__ int s_off[kListWarps][kListRanges + 1];
-  if (*unsorted) return;
+  if (unsorted && *unsorted) return;
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
   const int64_t item = (int64_t)blockIdx.x * kListWarps + wib;
@@ -735,6 +735,22 @@ int* parked_columns(const Geom& g, int* nbr, int64_t out_nnz) {
   return nbr ? nbr + (int64_t)(g.KV - 1) * out_nnz : nullptr;
 }
 
+// Pair lists of every (tile, offset) from a finished neighbour table.
+int launch_rule_lists(const int* out_zp, const Geom& g, int64_t out_nnz, int tnm, const int* nbr, int* rules,
+                      int* rule_size, const int* unsorted, int* status, cudaStream_t st) {
+  // enough warps to fill the machine, at most 32 offsets per warp (one running count per lane)
+  const int64_t lists = (int64_t)g.nTile * g.KV;
+  int kg = (int)(lists / 20000);
+  kg = kg < 3 ? 3 : kg > 32 ? 32 : kg;
+  if (kg > g.KV) kg = g.KV;
+  const int n_kg = div_up(g.KV, kg);
+  const int64_t items = (int64_t)g.nTile * n_kg;
+  rule_lists_kernel<<<(unsigned)div_up64(items, kListWarps), kListWarps * 32, 0, st>>>(
+      out_zp, g, out_nnz, tnm, kg, n_kg, nbr, rules, rule_size, unsorted, status);
+  SPH_LAUNCH_CHECK();
+  return SPH_OK;
+}
+
 // rows_parked: the column ids of the output rows are in parked_columns() (row-parallel path possible).
 int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int* out_zp, const Geom& g,
                 int64_t in_nnz, int64_t out_nnz, int tnm, int* rules, int* rule_size, int* nbr, int* nbr_t,
@@ -753,16 +769,8 @@ int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int
       SPH_LAUNCH_CHECK();
     }
     if (rule_size) {
-      // enough warps to fill the machine, at most 32 offsets per warp (one running count per lane)
-      const int64_t lists = (int64_t)g.nTile * g.KV;
-      int kg = (int)(lists / 20000);
-      kg = kg < 3 ? 3 : kg > 32 ? 32 : kg;
-      if (kg > g.KV) kg = g.KV;
-      const int n_kg = div_up(g.KV, kg);
-      const int64_t items = (int64_t)g.nTile * n_kg;
-      rule_lists_kernel<<<(unsigned)div_up64(items, kListWarps), kListWarps * 32, 0, st>>>(
-          out_zp, g, out_nnz, tnm, kg, n_kg, nbr, rules, rule_size, cm.unsorted, status);
-      SPH_LAUNCH_CHECK();
+      const int rc = launch_rule_lists(out_zp, g, out_nnz, tnm, nbr, rules, rule_size, cm.unsorted, status, st);
+      if (rc != SPH_OK) return rc;
     }
   }
   emit_rules_kernel<<<g.nTile, kEmitThreads, 0, st>>>(in_zi, in_zp, out_zi, out_zp, g, in_nnz, out_nnz, tnm, rules,
@@ -887,6 +895,20 @@ extern "C" int sph_rules_subm(const int32_t* d_z_idx, const int32_t* d_z_ptr, in
   if (rc != SPH_OK) return rc;
   return launch_emit(d_z_idx, d_z_ptr, d_z_idx, d_z_ptr, g, nnz, nnz, tile_n_max, d_rules, d_rule_size, d_nbr,
                      nullptr, cm, /*rows_parked=*/d_nbr != nullptr, fill_unused, d_status, (cudaStream_t)stream);
+}
+
+extern "C" int sph_rule_lists(const int32_t* d_oz_ptr, const sph_geom* s, int64_t out_nnz, const int32_t* d_nbr,
+                              int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int fill_unused,
+                              int32_t* d_status, void* stream) {
+  Geom g;
+  int rc = make_geom(s, &g);
+  if (rc != SPH_OK) return rc;
+  SPH_CHECK_ARG(d_oz_ptr && d_rules && d_rule_size && (out_nnz == 0 || d_nbr), "null argument");
+  SPH_CHECK_ARG(tile_n_max > 0 && out_nnz >= 0, "bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (fill_unused)
+    SPH_CUDA(cudaMemsetAsync(d_rules, 0xFF, (size_t)g.nTile * g.KV * 2 * (size_t)tile_n_max * sizeof(int), st));
+  return launch_rule_lists(d_oz_ptr, g, out_nnz, tile_n_max, d_nbr, d_rules, d_rule_size, nullptr, d_status, st);
 }
 
 // ---- allocation-free variant of sph_rules_subm ---------------------------------------------------

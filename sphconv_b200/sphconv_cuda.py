@@ -25,6 +25,7 @@ class config:
     fill_unused_rules = True   # -1 padding of `rules` as the reference (rules.cu:364-366)
     materialize_rules = True   # False: module path skips the padded `rules` tensor (rules/rule_size come back None)
     transposed_table = None    # None: build the dgrad table when grad mode is on; True/False forces it
+    overlap_rule_lists = True  # module path: write the reference-format pair lists on a side stream, beside the conv
 
 
 class _Tables:
@@ -51,11 +52,55 @@ def _check_common(zIndices, zPtr, dilation):
         raise RuntimeError("dilation != 1 is not supported")
 
 
+_side_streams = {}
+
+
+def _side_stream(dev):
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _side_streams.get(key)
+    if st is None:
+        st = torch.cuda.Stream(torch.device("cuda", key))
+        _side_streams[key] = st
+    return st
+
+
+def _lists_beside(dev, g, oz_ptr, out_nnz, nbr, tnm, rules, rule_size):
+    """The pair lists of a rule set whose table has been enqueued on the current stream, on the side stream: the
+    convolution kernels read the table only, so they can run while the lists are written.  `rules` carries the
+    event that marks the lists complete until `_join_lists` has ordered the current stream behind it."""
+    main = torch.cuda.current_stream(dev)
+    side = _side_stream(dev)
+    tables_done = torch.cuda.Event()
+    tables_done.record(main)
+    side.wait_event(tables_done)
+    with torch.cuda.device(dev):
+        C.check(C.lib().sph_rule_lists(C.ptr(oz_ptr), ctypes.byref(g), out_nnz, C.ptr(nbr), tnm, C.ptr(rules),
+                                       C.ptr(rule_size), int(config.fill_unused_rules), C.ptr(C.status_tensor(dev)),
+                                       ctypes.c_void_p(side.cuda_stream)))
+    lists_done = torch.cuda.Event()
+    lists_done.record(side)
+    for t in (rules, rule_size, nbr, oz_ptr):
+        t.record_stream(side)
+    rules._sph_ready = lists_done
+
+
+def _join_lists(rules):
+    """Orders the current stream behind the side-stream work that fills `rules` (if any is outstanding).  Called
+    by every op right AFTER it has enqueued its own kernel, so that kernel overlaps the lists and everything the
+    caller enqueues later sees them complete."""
+    ev = getattr(rules, "_sph_ready", None) if isinstance(rules, torch.Tensor) else None
+    if ev is not None:
+        torch.cuda.current_stream(rules.device).wait_event(ev)
+        rules._sph_ready = None
+
+
 def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
                    outSpatialShape: List[int], kernelSize: List[int], stride: List[int], padding: List[int],
-                   dilation: List[int], tileSize: List[int]):
+                   dilation: List[int], tileSize: List[int], defer_lists: bool = False):
     """ref: get_rules_subm, src/sphconv/rules.cu:326-390.  Returns [zIndices, zPtr, rules, ruleSize]
-    (the first two are the input objects, as in the reference)."""
+    (the first two are the input objects, as in the reference).  `defer_lists` (extension, used by the modules):
+    rules / ruleSize are written on a side stream and are complete on the current stream only after one of the
+    rule_conv* ops has been called with them."""
     _check_common(zIndices, zPtr, dilation)
     lib = C.lib()
     dev = zIndices.device
@@ -72,10 +117,13 @@ def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, s
     nbr = torch.empty((kv, nnz), dtype=torch.int32, device=dev)
     scratch_bytes = C.check(lib.sph_rules_subm_scratch_bytes(ctypes.byref(g), nnz))
     scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=dev) if scratch_bytes else None
+    defer = bool(defer_lists) and config.overlap_rule_lists and rules is not None and nnz > 0
     with torch.cuda.device(dev):
-        C.check(lib.sph_rules_subm(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), C.ptr(scratch), tnm, C.ptr(rules),
-                                   C.ptr(rule_size), C.ptr(nbr), int(config.fill_unused_rules),
-                                   C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+        C.check(lib.sph_rules_subm(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), C.ptr(scratch), tnm,
+                                   None if defer else C.ptr(rules), None if defer else C.ptr(rule_size), C.ptr(nbr),
+                                   int(config.fill_unused_rules), C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+    if defer:
+        _lists_beside(dev, g, zPtr, nnz, nbr, tnm, rules, rule_size)
     symmetric = all(int(k) % 2 == 1 and int(p) == int(k) // 2 and int(s) == 1
                     for k, p, s in zip(kernelSize, padding, stride))
     tables = _Tables(nbr, None, nnz, nnz, rules._version if rules is not None else 0, symmetric)
@@ -129,9 +177,11 @@ def get_rules_begin(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, 
 
 def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
               outSpatialShape: List[int], kernelSize: List[int], stride: List[int], padding: List[int],
-              dilation: List[int], tileSize: List[int], pending: Optional[PendingRules] = None):
+              dilation: List[int], tileSize: List[int], pending: Optional[PendingRules] = None,
+              defer_lists: bool = False):
     """ref: get_rules, src/sphconv/rules.cu:405-486.  Returns [ozIndices, ozPtr, rules, ruleSize].
-    `pending` (extension): the result of get_rules_begin on the same arguments; step 1 is then not run again."""
+    `pending` (extension): the result of get_rules_begin on the same arguments; step 1 is then not run again.
+    `defer_lists` (extension): as for get_rules_subm."""
     key = _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
     if pending is None or not pending.matches(zIndices, zPtr, key):
         pending = get_rules_begin(zIndices, zPtr, batchSize, spatialShape, outSpatialShape, kernelSize, stride,
@@ -157,9 +207,13 @@ def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatia
             rule_size = torch.empty((n_tile, kv), dtype=torch.int32, device=dev)
         nbr = torch.empty((kv, out_nnz), dtype=torch.int32, device=dev)
         nbr_t = torch.empty((kv, nnz), dtype=torch.int32, device=dev) if _want_transposed() else None
+        defer = bool(defer_lists) and config.overlap_rule_lists and rules is not None and out_nnz > 0
         C.check(lib.sph_rules_strided_fill(C.ptr(zIndices), C.ptr(zPtr), nnz, ctypes.byref(g), C.ptr(scratch),
-                                           C.ptr(oz_ptr), out_nnz, tnm, C.ptr(oz_idx), C.ptr(rules), C.ptr(rule_size),
+                                           C.ptr(oz_ptr), out_nnz, tnm, C.ptr(oz_idx),
+                                           None if defer else C.ptr(rules), None if defer else C.ptr(rule_size),
                                            C.ptr(nbr), C.ptr(nbr_t), int(config.fill_unused_rules), C.ptr(status), st))
+    if defer:
+        _lists_beside(dev, g, oz_ptr, out_nnz, nbr, tnm, rules, rule_size)
     tables = _Tables(nbr, nbr_t, nnz, out_nnz, rules._version if rules is not None else 0, False)
     if rules is not None:
         rules._sph = tables
@@ -247,7 +301,9 @@ def rule_conv(feature: torch.Tensor, weight: torch.Tensor, rules, ruleSize, outN
     """ref: rule_conv, src/sphconv/rule_conv.cu:286-336.  feature [NNZ,iC], weight [KV,iC,oC] ->
     [outNNZ,oC].  Keyword arguments are extensions (fused epilogue relu(acc*scale + bias), output dtype)."""
     tb = _tables_for(rules, ruleSize, feature.shape[0], int(outNNZ), need_t=False)
-    return _gather(feature, weight, tb.nbr, int(outNNZ), False, scale, bias, relu, out_dtype)
+    out = _gather(feature, weight, tb.nbr, int(outNNZ), False, scale, bias, relu, out_dtype)
+    _join_lists(rules)
+    return out
 
 
 def rule_conv_d_feature(feature: torch.Tensor, weight: torch.Tensor, rules, ruleSize,
@@ -277,6 +333,7 @@ def rule_conv_d_weight(feature: torch.Tensor, d_featureOut: torch.Tensor, rules,
         C.check(C.lib().sph_conv_wgrad(C.ptr(feature), C.ptr(d_featureOut), C.DTYPE_CODE[feature.dtype],
                                        feature.shape[0], C.ptr(tb.nbr), d_featureOut.shape[0], kv, k_ch, n_ch,
                                        C.ptr(dw), 1, C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+    _join_lists(rules)
     return dw
 
 

@@ -171,3 +171,46 @@ def test_sequential_starts_strided_rules_ahead():
     other = ops.get_rules(zi.clone(), zp, *geom[2:], pending=ops.get_rules_begin(*geom))
     for a, b, c in zip(want, got, other):
         assert torch.equal(a, b) and torch.equal(a, c)
+
+
+def test_module_rules_written_beside_the_convolution():
+    """The module path writes the reference-format pair lists on a side stream while the convolution runs; once the
+    layer has returned they are complete on the caller's stream and equal those of the plain ops."""
+    from sphconv_b200 import sphconv_cuda as ops
+    rng = np.random.default_rng(17)
+    B, shape = 3, [10, 14, 12]
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.3, False)        # unsorted columns too
+    feat = torch.as_tensor(rng.standard_normal((z_idx.shape[0], 16)), dtype=torch.float16, device=DEV)
+    zi, zp = torch.as_tensor(z_idx, device=DEV), torch.as_tensor(z_ptr, device=DEV)
+    sub = sphconv.SubMConv3d(16, 16, 3, indice_key="k").to(DEV).half().eval()
+    down = sphconv.SparseConv3d(16, 32, 3, stride=2, padding=1, indice_key="d").to(DEV).half().eval()
+
+    def canon(rules, rule_size):
+        r, n = rules.cpu().numpy(), rule_size.cpu().numpy()
+        out = {}
+        for t in range(r.shape[0]):
+            for k in range(r.shape[1]):
+                m = min(int(n[t, k]), r.shape[3])
+                out[(t, k)] = sorted(zip(r[t, k, 0, :m].tolist(), r[t, k, 1, :m].tolist()))
+        return n, out
+
+    for flag in (True, False):
+        ops.config.overlap_rule_lists = flag
+        try:
+            with torch.no_grad():
+                x = sphconv.SparseConvTensor(feat, shape, B, z_idx=zi, z_ptr=zp)
+                y = down(sub(x))
+                # a kernel of the caller's on the current stream, right behind the layers, already sees the lists
+                _, _, rules_s, size_s, _ = x.rule_cache["k"]
+                _, _, rules_d, size_d, _ = y.rule_cache["d"]
+                snap = (rules_s.clone(), size_s.clone(), rules_d.clone(), size_d.clone())
+            assert getattr(rules_s, "_sph_ready", None) is None and getattr(rules_d, "_sph_ready", None) is None
+        finally:
+            ops.config.overlap_rule_lists = True
+        want_s = ops.get_rules_subm(zi, zp, B, shape, shape, [3] * 3, [1] * 3, [1] * 3, [1] * 3, [2, 2])
+        want_d = ops.get_rules(zi, zp, B, shape, [5, 7, 6], [3] * 3, [2] * 3, [1] * 3, [1] * 3, [2, 2])
+        for (r, n), (wr, wn) in (((snap[0], snap[1]), (want_s[2], want_s[3])), ((snap[2], snap[3]), (want_d[2], want_d[3]))):
+            n_got, got = canon(r, n)
+            n_want, want = canon(wr, wn)
+            assert (n_got == n_want).all() and got == want
+    sphconv.check_status()
