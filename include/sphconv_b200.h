@@ -142,7 +142,10 @@ int sph_rules_strided_fill(const int32_t* d_z_idx, const int32_t* d_z_ptr, int64
  * reads only the table can call those with d_rules = NULL and run this step on another stream, beside the convolution.
  *   d_oz_ptr   int32 [B,oH,oW] of the OUTPUT tensor (z_ptr itself for a submanifold layer)
  *   d_nbr      int32 [KV, out_nnz]   tile_n_max, d_rules, d_rule_size, fill_unused: as for sph_rules_subm
- * Lists come out in ascending output row per batch, whatever the order inside the columns. */
+ * Lists come out in ascending output row per batch, whatever the order inside the columns.
+ * With d_rules = NULL only d_rule_size is written: the exact length of every list.  Its maximum is the tile_n_max
+ * that cannot overflow (the reference sizes the lists with a heuristic, rules.cu:21-28, and drops pairs silently
+ * when it is too small, rules.cu:217-224): count, read the maximum, allocate, call again. */
 int sph_rule_lists(const int32_t* d_oz_ptr, const sph_geom* g, int64_t out_nnz, const int32_t* d_nbr,
                    int32_t tile_n_max, int32_t* d_rules, int32_t* d_rule_size, int fill_unused, int32_t* d_status,
                    void* stream);

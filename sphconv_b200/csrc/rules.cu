@@ -903,11 +903,12 @@ extern "C" int sph_rule_lists(const int32_t* d_oz_ptr, const sph_geom* s, int64_
   Geom g;
   int rc = make_geom(s, &g);
   if (rc != SPH_OK) return rc;
-  SPH_CHECK_ARG(d_oz_ptr && d_rules && d_rule_size && (out_nnz == 0 || d_nbr), "null argument");
-  SPH_CHECK_ARG(tile_n_max > 0 && out_nnz >= 0, "bad sizes");
+  SPH_CHECK_ARG(d_oz_ptr && d_rule_size && (out_nnz == 0 || d_nbr), "null argument");
+  SPH_CHECK_ARG((d_rules == nullptr || tile_n_max > 0) && out_nnz >= 0, "bad sizes");
   cudaStream_t st = (cudaStream_t)stream;
-  if (fill_unused)
+  if (d_rules && fill_unused)
     SPH_CUDA(cudaMemsetAsync(d_rules, 0xFF, (size_t)g.nTile * g.KV * 2 * (size_t)tile_n_max * sizeof(int), st));
+  // without d_rules the kernel only counts: d_rule_size gets the exact list lengths
   return launch_rule_lists(d_oz_ptr, g, out_nnz, tile_n_max, d_nbr, d_rules, d_rule_size, nullptr, d_status, st);
 }
 

@@ -26,6 +26,7 @@ class config:
     materialize_rules = True   # False: module path skips the padded `rules` tensor (rules/rule_size come back None)
     transposed_table = None    # None: build the dgrad table when grad mode is on; True/False forces it
     overlap_rule_lists = True  # module path: write the reference-format pair lists on a side stream, beside the conv
+    exact_rule_capacity = False  # True: tile_n_max = the longest list (two passes + a host read), never an overflow
 
 
 class _Tables:
@@ -94,6 +95,23 @@ def _join_lists(rules):
         rules._sph_ready = None
 
 
+def _exact_lists(dev, g, oz_ptr, out_nnz, nbr, n_tile, kv):
+    """rules / rule_size sized by the longest list: count, read the maximum, allocate, fill (all on the current
+    stream).  The reference's heuristic capacity (rules.cu:21-28) can be too small, and then pairs are lost."""
+    lib = C.lib()
+    rule_size = torch.empty((n_tile, kv), dtype=torch.int32, device=dev)
+    status = C.status_tensor(dev)
+    with torch.cuda.device(dev):
+        st = C.stream_ptr(dev)
+        C.check(lib.sph_rule_lists(C.ptr(oz_ptr), ctypes.byref(g), out_nnz, C.ptr(nbr), 0, None, C.ptr(rule_size), 0,
+                                   C.ptr(status), st))
+        tnm = max(1, int(rule_size.max().item())) if rule_size.numel() else 1
+        rules = torch.empty((n_tile, kv, 2, tnm), dtype=torch.int32, device=dev)
+        C.check(lib.sph_rule_lists(C.ptr(oz_ptr), ctypes.byref(g), out_nnz, C.ptr(nbr), tnm, C.ptr(rules),
+                                   C.ptr(rule_size), int(config.fill_unused_rules), C.ptr(status), st))
+    return rules, rule_size
+
+
 def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
                    outSpatialShape: List[int], kernelSize: List[int], stride: List[int], padding: List[int],
                    dilation: List[int], tileSize: List[int], defer_lists: bool = False):
@@ -110,7 +128,8 @@ def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, s
     n_tile = C.check(lib.sph_num_tiles(ctypes.byref(g)))
     rules = rule_size = None
     tnm = 0
-    if config.materialize_rules:
+    exact = config.materialize_rules and config.exact_rule_capacity
+    if config.materialize_rules and not exact:
         tnm = C.check(lib.sph_tile_n_max(ctypes.byref(g), nnz))
         rules = torch.empty((n_tile, kv, 2, tnm), dtype=torch.int32, device=dev)
         rule_size = torch.empty((n_tile, kv), dtype=torch.int32, device=dev)
@@ -124,6 +143,8 @@ def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, s
                                    int(config.fill_unused_rules), C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
     if defer:
         _lists_beside(dev, g, zPtr, nnz, nbr, tnm, rules, rule_size)
+    if exact:
+        rules, rule_size = _exact_lists(dev, g, zPtr, nnz, nbr, n_tile, kv)
     symmetric = all(int(k) % 2 == 1 and int(p) == int(k) // 2 and int(s) == 1
                     for k, p, s in zip(kernelSize, padding, stride))
     tables = _Tables(nbr, None, nnz, nnz, rules._version if rules is not None else 0, symmetric)
@@ -201,7 +222,8 @@ def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatia
         oz_idx = torch.empty((out_nnz,), dtype=torch.int32, device=dev)
         rules = rule_size = None
         tnm = 0
-        if config.materialize_rules:
+        exact = config.materialize_rules and config.exact_rule_capacity
+        if config.materialize_rules and not exact:
             tnm = C.check(lib.sph_tile_n_max(ctypes.byref(g), nnz))
             rules = torch.empty((n_tile, kv, 2, tnm), dtype=torch.int32, device=dev)
             rule_size = torch.empty((n_tile, kv), dtype=torch.int32, device=dev)
@@ -214,6 +236,8 @@ def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatia
                                            C.ptr(nbr), C.ptr(nbr_t), int(config.fill_unused_rules), C.ptr(status), st))
     if defer:
         _lists_beside(dev, g, oz_ptr, out_nnz, nbr, tnm, rules, rule_size)
+    if exact:
+        rules, rule_size = _exact_lists(dev, g, oz_ptr, out_nnz, nbr, n_tile, kv)
     tables = _Tables(nbr, nbr_t, nnz, out_nnz, rules._version if rules is not None else 0, False)
     if rules is not None:
         rules._sph = tables

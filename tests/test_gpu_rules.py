@@ -110,6 +110,40 @@ def test_overflow_is_flagged_and_tables_stay_exact():
     assert_tables_match(res, rules, z_idx.shape[0], z_idx.shape[0])
 
 
+@pytest.mark.parametrize("subm", [True, False])
+def test_exact_rule_capacity_never_overflows(subm):
+    """config.exact_rule_capacity: tile_n_max is the longest list (counted first), so the input that overflows the
+    reference's heuristic capacity keeps every pair and raises no status bit."""
+    from sphconv_b200 import sphconv_cuda as ops
+    B, shape = 2, [16, 16, 64]
+    occ = np.zeros((B, *shape), bool)
+    occ[:, :2, :2, :] = True
+    occ[1, 7, 9, 3] = True
+    z_ptr = np.cumsum(occ.sum(axis=3).reshape(-1)).astype(np.int32).reshape(B, 16, 16)
+    z_idx = np.nonzero(occ)[3].astype(np.int32)
+    ks, st, pd = ([3, 3, 3], [1, 1, 1], [1, 1, 1]) if subm else ([3, 3, 3], [2, 2, 2], [1, 1, 1])
+    res = oracle_rules(z_idx, z_ptr, B, shape, ks, st, pd, [2, 2], subm)
+    check_status()
+    ops.config.exact_rule_capacity = True
+    try:
+        _, _, _, oz_idx, oz_ptr, rules, rule_size = gpu_rules(z_idx, z_ptr, B, shape, ks, st, pd, [2, 2], subm)
+    finally:
+        ops.config.exact_rule_capacity = False
+    assert check_status() == 0
+    if subm:
+        assert res["rule_size"].max() > res["tile_n_max"], "the case must overflow the heuristic capacity"
+    assert rules.shape[3] == res["rule_size"].max()
+    rs, r = rule_size.cpu().numpy(), rules.cpu().numpy()
+    assert (rs == res["rule_size"]).all()
+    got = set()
+    for t, k in zip(*np.nonzero(rs)):
+        n = rs[t, k]
+        got.update((int(k), int(i), int(o)) for i, o in zip(r[t, k, 0, :n], r[t, k, 1, :n]))
+    want = set(zip(res["k"].tolist(), res["in"].tolist(), res["out"].tolist()))
+    assert got == want and len(want) == int(rs.sum())
+    assert_tables_match(res, rules, z_idx.shape[0], oz_idx.shape[0])
+
+
 @pytest.mark.parametrize("name,batch", [("cfg1", 1), ("cfg2", 4), ("cfg3", 2)])
 def test_config_first_layer(name, batch):
     """BASELINE configs at full per-scan size: first layer's rule set (cfg1 SubM; cfg2 strided; cfg3 SubM)."""
