@@ -222,7 +222,7 @@ int sph_to_dense(void* d_rows, int32_t row_bytes, int64_t nnz, const int32_t* d_
 /* Backward of the fused epilogue relu(acc + bias) of sph_conv_gather (an extension: the reference applies no bias or
  * activation).  d_dpre[r][c] = d_out[r][c] > 0 ? d_dout[r][c] : 0 (relu != 0; else a copy) and
  * d_dbias[c] = sum over rows of d_dpre[r][c] (fp32 [channels], overwritten; may be null, as may d_dpre).
- * dtype SPH_F32 / SPH_F16 / SPH_BF16; `channels` must divide 256. */
+ * dtype SPH_F32 / SPH_F16 / SPH_BF16; at most 256 channels. */
 int sph_epilogue_backward(const void* d_dout, const void* d_out, int dtype, int64_t n, int32_t channels, int relu,
                           void* d_dpre, float* d_dbias, void* stream);
 

@@ -1,6 +1,7 @@
 """Builds the reference's own CUDA implementation of the path as a checker: oracle/_ref/sphconv_ref*.so.
 
-Sources are compiled where they lie in the reference tree (the directory named by REFERENCE_ROOT):
+Sources are compiled where they lie in the reference tree (the directory named by the environment variable
+REFERENCE_ROOT, else a directory "reference" beside this repository):
 src/sphconv/rules.cu and src/sphconv/tensor.cu unmodified, plus - when a CUTLASS header tree is found -
 src/sphconv/rule_conv.cu.  The reference pins no CUTLASS version (its submodule directory is empty); the
 only copy on this machine is a 4.x tree whose MmaPipelined calls `iterator.clear_mask(bool)`, so the build
@@ -23,7 +24,8 @@ import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+# The reference tree: the directory the environment names, else a checkout called "reference" beside this repository.
+REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

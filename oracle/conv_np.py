@@ -10,8 +10,19 @@ Test infrastructure; never imported by the product.
   (src/sphconv/rule_conv.cu:469-518, the per-tile partials are summed at line 517)
 
 ``pairs`` is the canonical table [(tile, k, in, out)] from ``rules_np``; arithmetic is float64 unless asked otherwise.
+
+Inside one kernel offset k the map input row <-> output row is one-to-one (an output voxel and an offset name
+exactly one input voxel, src/sphconv/rules.cu:124-133), so the scatter of one offset has no repeated target and is a
+plain indexed add; ``np.add.at`` is kept behind ``unique_per_k=False`` for pair tables that do not come from rules.
 """
 import numpy as np
+
+
+def _scatter_add(dst, idx, val, unique):
+    if unique:
+        dst[idx] += val
+    else:
+        np.add.at(dst, idx, val)
 
 
 def _by_k(pairs, KV):
@@ -22,23 +33,23 @@ def _by_k(pairs, KV):
             yield k, pairs[sel, 2], pairs[sel, 3]
 
 
-def conv_forward(feature, weight, pairs, out_nnz, dtype=np.float64):
+def conv_forward(feature, weight, pairs, out_nnz, dtype=np.float64, unique_per_k=True):
     """feature [NNZ,iC], weight [KV,iC,oC] -> [out_nnz,oC]."""
     f = np.asarray(feature, dtype=dtype)
     w = np.asarray(weight, dtype=dtype)
     out = np.zeros((out_nnz, w.shape[2]), dtype=dtype)
     for k, i, o in _by_k(pairs, w.shape[0]):
-        np.add.at(out, o, f[i] @ w[k])
+        _scatter_add(out, o, f[i] @ w[k], unique_per_k)
     return out
 
 
-def conv_dgrad(d_out, weight, pairs, nnz, dtype=np.float64):
+def conv_dgrad(d_out, weight, pairs, nnz, dtype=np.float64, unique_per_k=True):
     """d_out [outNNZ,oC], weight [KV,iC,oC] (un-transposed) -> d_feature [nnz,iC]."""
     g = np.asarray(d_out, dtype=dtype)
     w = np.asarray(weight, dtype=dtype)
     dx = np.zeros((nnz, w.shape[1]), dtype=dtype)
     for k, i, o in _by_k(pairs, w.shape[0]):
-        np.add.at(dx, i, g[o] @ w[k].T)
+        _scatter_add(dx, i, g[o] @ w[k].T, unique_per_k)
     return dx
 
 

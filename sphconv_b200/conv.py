@@ -102,6 +102,13 @@ class Conv3d(Convolution):
             oz_idx, oz_ptr, rules, rule_size = ops.get_rules(*args, pending=pending, defer_lists=True)
         return oz_idx, oz_ptr, rules, rule_size, get_tile_grid_shape(out_shape, self.tile_size)
 
+    def _rule_meta(self, input, in_shape, out_shape):
+        """Sizes a timed rule-generation section carries (for byte accounting by whoever reads the timings)."""
+        tg = get_tile_grid_shape(out_shape, self.tile_size)
+        return dict(subm=self.subm, n_in=input.feature.shape[0], B=input.B, in_shape=list(in_shape),
+                    out_shape=list(out_shape), n_tile=tg[0] * tg[1],
+                    kv=self.kernel_size[0] * self.kernel_size[1] * self.kernel_size[2])
+
     def begin_rules(self, input: SparseConvTensor):
         """Extension used by Sequential: enqueue the first step of this (strided) layer's rule generation on a tensor
         that has the geometry this layer will see - the input of the submanifold layer in front of it - so that
@@ -112,7 +119,7 @@ class Conv3d(Convolution):
         in_shape = [input.D, input.W, input.H]
         out_shape = out_spatial(in_shape, self.kernel_size, self.stride, self.padding, self.dilation)
         tag = self.name or "conv{}_{}".format(self.in_channels, self.weight.shape[4])
-        with profiling.section("rules:" + tag, subm=False, n_in=input.feature.shape[0]):
+        with profiling.section("rules:" + tag, **self._rule_meta(input, in_shape, out_shape)):
             input.rule_cache[("pending", id(self))] = ops.get_rules_begin(
                 input.z_idx, input.z_ptr, input.B, in_shape, out_shape, self.kernel_size, self.stride, self.padding,
                 self.dilation, self.tile_size)
@@ -130,7 +137,8 @@ class Conv3d(Convolution):
         tag = self.name or "{}{}_{}".format("subm" if self.subm else "conv", in_channels, out_channels)
         datas = input.find_rule(self.indice_key) if self.indice_key is not None else None
         if datas is None:
-            with profiling.section("rules:" + tag, subm=self.subm, n_in=input.feature.shape[0]):
+            profiling.current_rule_tag = tag
+            with profiling.section("rules:" + tag, **self._rule_meta(input, in_shape, out_shape)):
                 datas = self._rules(input, in_shape, out_shape)
             if self.indice_key is not None:
                 input.rule_cache[self.indice_key] = datas
@@ -145,8 +153,12 @@ class Conv3d(Convolution):
         if needs_grad:
             profiling.current_tag = tag
             # bias and activation run in the kernel's epilogue in training too (extension arguments of ConvFunction)
+            mw = getattr(self.weight, "_sph_master_grad", None)      # slices of a sharding.GradBuffer, if attached
+            mb = getattr(bias, "_sph_master_grad", None) if bias is not None else None
+            master = None if mw is None and mb is None else \
+                (None if mw is None else mw.view(-1, in_channels, out_channels), mb)
             out_feature = ConvFunction.apply(input.feature, weight, rules, rule_size, tile_grid_shape,
-                                             oz_idx.shape[0], bias, self.activation == 'relu')
+                                             oz_idx.shape[0], bias, self.activation == 'relu', master)
         else:
             weight = self._cached_packed(weight)
             with profiling.section("conv:" + tag, iC=in_channels, oC=out_channels, n_in=input.feature.shape[0],

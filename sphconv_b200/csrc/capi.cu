@@ -20,6 +20,25 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+int current_sm_count() {
+  constexpr int kMaxDev = 64;
+  static std::atomic<int> s_sms[kMaxDev];     // zero-initialised; a racing first call writes the same value twice
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    set_error("current_sm_count: cudaGetDevice failed");
+    return 0;
+  }
+  int n = (dev >= 0 && dev < kMaxDev) ? s_sms[dev].load(std::memory_order_relaxed) : 0;
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      set_error("current_sm_count: cudaDeviceGetAttribute failed");
+      return 0;
+    }
+    if (dev >= 0 && dev < kMaxDev) s_sms[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
 // conv_generic.cu
 int conv_gather_generic(const void* rows, int dtype, int64_t n_rows, const void* weight, const int* nbr,
                         int64_t n_out, int kv, int K, int N, int flip_k, const float* scale, const float* bias,

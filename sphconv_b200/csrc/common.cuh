@@ -54,6 +54,9 @@ inline int dtype_bytes(int dtype) {
   }
 }
 
+// Multiprocessor count of the CURRENT device (cached per device ordinal, thread-safe); 0 with the error set on failure.
+int current_sm_count();
+
 // Geometry in the form the kernels take by value.
 struct Geom {
   int B, H, W, D, oH, oW, oD;

@@ -27,8 +27,6 @@
 // rows: core (row group g, chunk c) at c*4112 + g*128; weights: core (channel group gn, chunk c) at
 // c*(N/8)*128 + gn*128 (images hold the N real channels only: the rows up to M = 64/128 that the instruction also
 // reads are whatever follows in shared memory and only feed accumulator rows nobody reads).
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -47,7 +45,6 @@ constexpr int kProducerWarps = SPH_TC_PRODUCER_WARPS;    // gather warps
 #ifndef SPH_GK4
 #define SPH_GK4 3                   // kernel offsets per pipeline stage for 64-byte rows
 #endif
-constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kTcThreads = (kProducerWarps + 1 + 4) * 32;
 constexpr int kSubRows = 64;        // accumulator columns (output rows) an epilogue thread reads back at a time
@@ -128,25 +125,6 @@ __device__ __forceinline__ void store_rows64_any(uint8_t* dst, int row_pitch, in
   }
 }
 
-// Developer instrumentation (-DSPH_TC_PROF): per-CTA cycle counts of each warp role and of its barrier waits.
-#ifdef SPH_TC_PROF
-__device__ long long g_tc_prof[256][12];
-#define SPH_PROF_BEGIN() long long prof_begin = clock64(), prof_t0 = 0, prof_acc[3] = {0, 0, 0}
-#define SPH_PROF_T0() prof_t0 = clock64()
-#define SPH_PROF_ADD(i) prof_acc[i] += clock64() - prof_t0
-#define SPH_PROF_END(base, pred)                                                     \
-  if ((pred) && blockIdx.x < 256) {                                                  \
-    g_tc_prof[blockIdx.x][(base) + 0] = clock64() - prof_begin;                      \
-    g_tc_prof[blockIdx.x][(base) + 1] = prof_acc[1];                                 \
-    g_tc_prof[blockIdx.x][(base) + 2] = prof_acc[2];                                 \
-  }
-#else
-#define SPH_PROF_BEGIN()
-#define SPH_PROF_T0()
-#define SPH_PROF_ADD(i)
-#define SPH_PROF_END(base, pred)
-#endif
-
 // KC = 16-byte chunks per gathered row (2, 4, 8, 16), I8 = int8 operands.  Both are compile-time so that the
 // per-stage instruction streams of the gather warps and of the MMA thread have no loops or branches to
 // resolve: with two or three warps per scheduler nothing hides a lone warp's instruction latency, and those
@@ -215,7 +193,14 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
     constexpr int wpg = kProducerWarps / G;        // warps per team
     const int grp = warp / wpg, wig = warp % wpg;
     constexpr int RPW = kTileRows / wpg;           // rows of each stage this warp gathers
-    constexpr int RPL = RPW * LPR / 32;            // consecutive rows per lane (LPR lanes share a row)
+    constexpr int RPL = RPW * LPR / 32;            // rows per lane and offset (LPR lanes share a row)
+    // One gather instruction covers NG consecutive rows: lane group q = lane / LPR takes rows q, q + NG, ...  A row
+    // is 16 bytes further in each chunk plane and a chunk plane is kRowsLbo = 16 mod 128 bytes further, so lane
+    // (q, c) writes bank group (q + c) mod 8 and the 32 lanes spread evenly over all banks (with groups RPL rows
+    // apart, i.e. a multiple of 128 bytes, the 64- and 32-byte rows used half and a quarter of the banks).
+    // Consecutive output rows also tend to have consecutive input rows as neighbours: fewer cache lines per
+    // instruction.
+    constexpr int NG = 32 / LPR;
     if (p.w_resident && tid == 0) {
       mbar_arrive_expect_tx(smem_u32(&s_w_full), (uint32_t)(p.kv * p.w_bytes));
       for (int k = 0; k < p.kv; ++k)   // one bulk copy per offset keeps each transfer small
@@ -250,7 +235,10 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
         const int f = f0 + (idx / eps) * G;
         const int rem = idx % eps;
         const int k = (f - ti * groups) * GK + rem / RPW;
-        const int64_t r = r0 + (rem & (RPW - 1));
+        // slot -> row: lane group q keeps its RPL slots together (vector reads of the parked table), and its j-th slot
+        // is row q + j * NG of the warp's rows, so that one gather instruction covers NG consecutive rows
+        const int slot = rem & (RPW - 1);
+        const int64_t r = r0 + (slot % RPL) * NG + slot / RPL;
         // plain loads with no dependent work here: all 32 stay in flight; they are checked when parked
         ent[e] = (ti < my_tiles && f < f_end && k < p.kv && r < p.n_out)
                      ? __ldg(p.nbr + (int64_t)(p.flip_k ? p.kv - 1 - k : k) * p.n_out + r) : -1;
@@ -270,14 +258,13 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
       __syncwarp();
     };
     const int l_chunk = lane % LPR;
-    const int l_row0 = (lane / LPR) * RPL;         // first of this lane's rows inside the warp's RPW
-    const uint32_t lane_dst = (uint32_t)l_chunk * kRowsLbo + (uint32_t)(wig * RPW + l_row0) * 16u;
+    const int l_grp = lane / LPR;                  // this lane's rows inside the warp's RPW: l_grp + j * NG
+    const int l_slot0 = l_grp * RPL;               // its first slot in the parked table
+    const uint32_t lane_dst = (uint32_t)l_chunk * kRowsLbo + (uint32_t)(wig * RPW + l_grp) * 16u;
     const uint8_t* rows_c = rows + l_chunk * 16;
     const uint32_t row_bytes = (uint32_t)KC * 16u;
     const uint32_t stage0_u = smem_u32(stage0);
     const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
-
-    SPH_PROF_BEGIN();
     int s = grp % S;                                // slot of flat stage f is f % S
     uint32_t par = ((uint32_t)(grp / S) & 1u) ^ 1u; // parity to wait for on the slot's empty barrier
     int ti = 0;                                     // tile of the current stage
@@ -301,19 +288,16 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
       // slots in order, so "the slot of my stage after next is free" implies the slot of this one is too.
       if (credits == 0) {
         bool ok_w = true;
-        SPH_PROF_T0();
         if (lane == 0) {
           int sa = s + (batch - 1) * G;
           uint32_t pa = par;
           if (sa >= S) { sa -= S; pa ^= 1u; }
           ok_w = mbar_wait(empty0 + 8u * sa, pa, abort_flag);
         }
-        SPH_PROF_ADD(1);
         if (__any_sync(0xffffffffu, !ok_w)) break;   // also orders the other lanes behind the poll
         credits = batch;
       }
       --credits;
-      SPH_PROF_T0();
       const uint32_t stage = stage0_u + (uint32_t)(s * stage_bytes);
       const int k0 = (f - (tile_end - groups)) * GK;
       if (!p.w_resident && wig == 0 && lane == 0) {
@@ -324,7 +308,7 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
 #pragma unroll
       for (int g = 0; g < GK; ++g) {
         if (GK == 1 || k0 + g < p.kv) {
-          const int* trow = tbl + own_j * eps + g * RPW + l_row0;
+          const int* trow = tbl + own_j * eps + g * RPW + l_slot0;
           const uint32_t dst0 = stage + (uint32_t)g * X_BYTES + lane_dst;
 #pragma unroll
           for (int j0 = 0; j0 < RPL; j0 += LPR) {
@@ -347,19 +331,17 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
               const uint32_t sz = present ? 16u : 0u;
               // .ca: the three depth offsets of one (kh,kw) read nearly the same input rows a stage or two
               // apart, and the slice of L1 that the shared-memory carve-out leaves catches most of the repeats
-              cp_async_16_ca(dst0 + (uint32_t)(j0 + j) * 16u, src, sz);
-              if (PASSES == 2) cp_async_16_ca(dst0 + (uint32_t)(j0 + j) * 16u + 8u * kRowsLbo, src + 128, sz);
+              cp_async_16_ca(dst0 + (uint32_t)((j0 + j) * NG) * 16u, src, sz);
+              if (PASSES == 2) cp_async_16_ca(dst0 + (uint32_t)((j0 + j) * NG) * 16u + 8u * kRowsLbo, src + 128, sz);
             }
           }
         }
       }
-      SPH_PROF_ADD(2);
       cp_async_arrive_noinc(full0 + 8u * s);
       ++own_j;
       s += G;
       if (s >= S) { s -= S; par ^= 1u; }
     }
-    SPH_PROF_END(0, tid == 0);
     cp_async_wait_all();
     if (bad && p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
   } else if (warp == kMmaWarp) {
@@ -383,23 +365,20 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
       const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
       bool dead = false;
       if (p.w_resident) dead = !mbar_wait(smem_u32(&s_w_full), 0u, abort_flag);
-      SPH_PROF_BEGIN();
       int s = 0;
       uint32_t par = 0u;                                          // parity to wait for on the full barriers
       uint32_t x_lo = x_lo_first;
       for (int ti = 0; ti < my_tiles && !dead; ++ti) {
         const int buf = ti & 1;
-        SPH_PROF_T0();
         if (!mbar_wait(smem_u32(&s_acc_empty[buf]), (((uint32_t)ti >> 1) & 1u) ^ 1u, abort_flag)) break;
-        SPH_PROF_ADD(2);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTileRows);
         uint32_t accumulate = 0u;
         uint32_t w_lo = w_lo_res;
         for (int k0 = 0; k0 < p.kv; k0 += GK) {
-          SPH_PROF_T0();
           if (!mbar_wait(full0 + 8u * s, par, abort_flag)) { dead = true; break; }
-          SPH_PROF_ADD(1);
+          // the gather warps wrote the stage with cp.async (generic proxy); the MMA reads it through the async proxy
+          fence_proxy_async();
           tc_fence_after();
           const uint32_t wl0 = p.w_resident ? w_lo : x_lo + w_in_stage;
 #pragma unroll
@@ -422,7 +401,6 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
         }
         if (!dead) umma_commit(smem_u32(&s_acc_full[buf]));
       }
-      SPH_PROF_END(4, true);
     }
     __syncwarp();
   } else {
@@ -434,14 +412,11 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
     const float sc = (has_oc && p.scale) ? __ldg(p.scale + oc) : 1.f;
     const float bi = (has_oc && p.bias) ? __ldg(p.bias + oc) : 0.f;
     const int row_pitch = p.N * p.out_esize;      // bytes of one output row
-    SPH_PROF_BEGIN();
     for (int ti = 0; ti < my_tiles; ++ti) {
       const int buf = ti & 1;
       const int64_t tile = (int64_t)blockIdx.x + (int64_t)ti * gridDim.x;
       bool ok = true;
-      SPH_PROF_T0();
       if (lane == 0) ok = mbar_wait(smem_u32(&s_acc_full[buf]), ((uint32_t)ti >> 1) & 1u, abort_flag, 128u);
-      SPH_PROF_ADD(1);
       if (__any_sync(0xffffffffu, !ok)) break;    // warp-uniform: tcgen05.ld is warp-wide
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTileRows);
@@ -461,7 +436,6 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_acc_empty[buf]));
     }
-    SPH_PROF_END(8, q == 0 && lane == 0);
   }
 
   // ---- wind down: every thread arrives here, also after an abort
@@ -522,8 +496,6 @@ bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   p->stage_off = off;
   const int stage_bytes = gk * (p->x_bytes + (p->w_resident ? 0 : p->w_bytes));
   if (stages < 2) return false;
-  const char* st_env = getenv("SPH_TC_STAGES");
-  if (st_env && atoi(st_env) >= 2 && atoi(st_env) <= stages) stages = atoi(st_env);
   p->stages = stages;
   const int gpt = (kv + gk - 1) / gk;               // stages per tile
   if (((gpt + 1) / 2) * gk * 64 > 32 * 32) return false;   // 32 table entries per lane and tile
@@ -579,12 +551,8 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
     set_error("conv_gather_tc: operands do not fit in shared memory");
     return SPH_ERR_UNSUPPORTED;
   }
-  static int s_sms = 0;
-  if (s_sms == 0) {
-    int dev = 0;
-    SPH_CUDA(cudaGetDevice(&dev));
-    SPH_CUDA(cudaDeviceGetAttribute(&s_sms, cudaDevAttrMultiProcessorCount, dev));
-  }
+  const int s_sms = current_sm_count();
+  if (s_sms <= 0) return SPH_ERR_CUDA;
   // every CTA takes all 512 TMEM columns, so exactly one is resident per SM
   int grid = s_sms < p.num_tiles ? s_sms : p.num_tiles;
   if (grid < 1) return SPH_OK;
@@ -637,9 +605,3 @@ int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cu
 }
 
 }  // namespace sph
-
-#ifdef SPH_TC_PROF
-extern "C" int sph_debug_tc_prof(long long* host_out /*[256*12]*/) {
-  return (int)cudaMemcpyFromSymbol(host_out, sph::g_tc_prof, sizeof(long long) * 256 * 12);
-}
-#endif

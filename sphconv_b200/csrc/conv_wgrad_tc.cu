@@ -16,8 +16,6 @@
 //
 // Warps 0-7 copy (dY tile once per tile, one batch of X tiles per stage), warp 8 issues the MMAs; the final flush is
 // done by warps 0-3.  Same bounded waits and abort path as the forward kernel.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -319,12 +317,8 @@ int conv_wgrad_tc(const void* rows, const void* dout, int dtype, int64_t n_rows,
   p.is_bf16 = dtype == SPH_BF16;
   p.status = status;
   p.num_tiles = (int)div_up64(n_out, kTileRows);
-  static int s_sms = 0;
-  if (s_sms == 0) {
-    int dev = 0;
-    SPH_CUDA(cudaGetDevice(&dev));
-    SPH_CUDA(cudaDeviceGetAttribute(&s_sms, cudaDevAttrMultiProcessorCount, dev));
-  }
+  const int s_sms = current_sm_count();
+  if (s_sms <= 0) return SPH_ERR_CUDA;
   int slices = s_sms / p.groups;
   if (slices > p.num_tiles) slices = p.num_tiles;
   if (slices < 1) slices = 1;

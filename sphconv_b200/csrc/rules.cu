@@ -11,6 +11,7 @@
 //    (in,out) pairs to consecutive slots of its own list, so list order is deterministic
 //    (ascending output row inside a batch, batches in order) and no global atomics are used;
 //  * the same pass fills the neighbour tables nbr[k][out] / nbr_t[k][in] the convolution kernels read.
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -265,11 +266,18 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, Geom g, int64_t in_nnz,
-                int64_t out_nnz, int* nbr, int* __restrict__ nbr_t, ColMask cm) {
+                int64_t out_nnz, int* nbr, int* __restrict__ nbr_t, ColMask cm, int* __restrict__ status) {
   if (*cm.unsorted) return;
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= out_nnz) return;
   const int c = nbr[(int64_t)(g.KV - 1) * out_nnz + r];
+  // A row nobody parked a column id for (the caller's row count exceeds the prefix total) holds whatever the buffer
+  // held: it gets no neighbours and the status bit, instead of reads outside the index.
+  if ((unsigned)c >= (unsigned)(g.B * g.oH * g.oW)) {
+    for (int k = 0; k < g.KV; ++k) nbr[(int64_t)k * out_nnz + r] = -1;
+    if (status) atomicOr(status, SPH_STATUS_BAD_INDEX);
+    return;
+  }
   const int oy = c % g.oW;
   const int t2 = c / g.oW;
   const int ox = t2 % g.oH;
@@ -765,7 +773,7 @@ int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int
   if (fast) {
     if (out_nnz > 0) {
       nbr_rows_kernel<<<(unsigned)div_up64(out_nnz, 256), 256, 0, st>>>(in_zp, out_zi, g, in_nnz, out_nnz, nbr, nbr_t,
-                                                                         cm);
+                                                                         cm, status);
       SPH_LAUNCH_CHECK();
     }
     if (rule_size) {
@@ -923,7 +931,7 @@ extern "C" int sph_rules_subm_static(const int32_t* d_z_idx, const int32_t* d_z_
                                      int32_t* d_rule_size, int32_t* d_nbr, int fill_unused, int32_t* d_status,
                                      void* stream) {
   constexpr int kMaxDevices = 64;
-  static void* s_addr[kMaxDevices] = {nullptr};
+  static std::atomic<void*> s_addr[kMaxDevices];   // zero-initialised; two threads racing on the first call store the same address
   Geom g;
   int rc = make_geom(s, &g);
   if (rc != SPH_OK) return rc;
@@ -939,13 +947,17 @@ extern "C" int sph_rules_subm_static(const int32_t* d_z_idx, const int32_t* d_z_
     set_error("sph_rules_subm_static: device ordinal %d not supported", dev);
     return SPH_ERR_LIMIT;
   }
-  if (s_addr[dev] == nullptr) {
-    void* ptr = nullptr;
-    SPH_CUDA(cudaGetSymbolAddress(&ptr, g_subm_static_scratch));
-    s_addr[dev] = ptr;
+  void* scratch = s_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
+    SPH_CUDA(cudaGetSymbolAddress(&scratch, g_subm_static_scratch));
+    if (scratch == nullptr) {
+      set_error("sph_rules_subm_static: the built-in buffer has no device address");
+      return SPH_ERR_CUDA;
+    }
+    s_addr[dev].store(scratch, std::memory_order_release);
   }
   // the index is rebuilt (cleared first) by every call; nothing is carried over from the previous one
-  return sph_rules_subm(d_z_idx, d_z_ptr, nnz, s, s_addr[dev], tile_n_max, d_rules, d_rule_size, d_nbr, fill_unused,
+  return sph_rules_subm(d_z_idx, d_z_ptr, nnz, s, scratch, tile_n_max, d_rules, d_rule_size, d_nbr, fill_unused,
                         d_status, stream);
 }
 
@@ -992,12 +1004,12 @@ constexpr int kCountSlots = 256;
 struct CountRing {
   int32_t* host = nullptr;
   int32_t* dev = nullptr;
+  unsigned next = 0;          // per device: a word is reused only after kCountSlots - 1 further calls on ITS device
 };
 int count_slot(int32_t** host_word, int32_t** dev_word) {
   constexpr int kMaxDevices = 64;
   static CountRing rings[kMaxDevices];
   static std::mutex mu;
-  static unsigned next = 0;
   int dev = 0;
   SPH_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) {
@@ -1014,7 +1026,7 @@ int count_slot(int32_t** host_word, int32_t** dev_word) {
     r.host = (int32_t*)h;
     r.dev = (int32_t*)d;
   }
-  const unsigned slot = next++ % kCountSlots;
+  const unsigned slot = r.next++ % kCountSlots;
   *host_word = r.host + slot;
   *dev_word = r.dev + slot;
   return SPH_OK;

@@ -223,8 +223,9 @@ __device__ __forceinline__ void st_f(__nv_bfloat16* p, int64_t i, float v) { p[i
 constexpr int kEpiThreads = 256;
 
 // d_pre[r][c] = out[r][c] > 0 ? d_out[r][c] : 0 (relu) or d_out (no relu); d_bias[c] += sum_r d_pre[r][c].
-// A thread stays on one channel (C divides the block size), walks rows with a grid stride and keeps its sum in a
-// register; sums of equal channels meet in shared memory, one atomic per channel and block.
+// A thread stays on one channel (the first floor(256 / C) * C threads of a block work, the rest only join the
+// barrier), walks rows with a grid stride and keeps its sum in a register; sums of equal channels meet in shared
+// memory, one atomic per channel and block.
 template <typename T>
 __global__ void __launch_bounds__(kEpiThreads)
 epilogue_backward_kernel(const T* __restrict__ d_out, const T* __restrict__ out, int64_t n, int C, int relu,
@@ -232,8 +233,10 @@ epilogue_backward_kernel(const T* __restrict__ d_out, const T* __restrict__ out,
   __shared__ float s_sum[kEpiThreads];
   const int c = threadIdx.x % C;
   const int rows_per_block = kEpiThreads / C;
+  const int active = rows_per_block * C;
   float sum = 0.f;
-  for (int64_t r = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / C; r < n; r += (int64_t)gridDim.x * rows_per_block) {
+  for (int64_t r = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / C; r < n && (int)threadIdx.x < active;
+       r += (int64_t)gridDim.x * rows_per_block) {
     const int64_t i = r * C + c;
     float g = ld_f(d_out, i);
     if (relu && !(ld_f(out, i) > 0.f)) g = 0.f;
@@ -245,7 +248,7 @@ epilogue_backward_kernel(const T* __restrict__ d_out, const T* __restrict__ out,
     __syncthreads();
     if (threadIdx.x < C) {
       float t = 0.f;
-      for (int j = threadIdx.x; j < kEpiThreads; j += C) t += s_sum[j];
+      for (int j = threadIdx.x; j < active; j += C) t += s_sum[j];
       atomicAdd(d_bias + threadIdx.x, t);
     }
   }
@@ -258,7 +261,7 @@ extern "C" int sph_epilogue_backward(const void* d_dout, const void* d_out, int 
                                      int relu, void* d_dpre, float* d_dbias, void* stream) {
   SPH_CHECK_ARG(n >= 0 && channels > 0, "bad sizes");
   SPH_CHECK_ARG(dtype == SPH_F32 || dtype == SPH_F16 || dtype == SPH_BF16, "unsupported dtype");
-  SPH_CHECK_ARG(channels <= kEpiThreads && kEpiThreads % channels == 0, "channel count must divide 256");
+  SPH_CHECK_ARG(channels <= kEpiThreads, "at most 256 channels");
   cudaStream_t st = (cudaStream_t)stream;
   if (d_dbias) SPH_CUDA(cudaMemsetAsync(d_dbias, 0, (size_t)channels * sizeof(float), st));
   if (n == 0) return SPH_OK;

@@ -17,12 +17,15 @@ class ConvFunction(torch.autograd.Function):
     Two optional trailing arguments (extensions): ``bias`` [oC] and ``relu``.  With them the kernel's epilogue
     computes relu(acc + bias) in fp32 before the single rounding to the output dtype, and backward masks the incoming
     gradient with (output > 0) and returns the bias gradient, so a training step needs no separate bias-add and
-    activation passes over the output."""
+    activation passes over the output.  ``master`` (extension): (d_weight fp32 [KV,iC,oC] or None, d_bias fp32 [oC]
+    or None) slices of a caller-owned fp32 gradient buffer (sharding.GradBuffer); backward then ACCUMULATES the fp32
+    gradients there and returns None for them, so nothing is rounded to the feature dtype on the way."""
 
     @staticmethod
     def forward(ctx, feature: torch.Tensor, weight: torch.Tensor, rules, rule_size, tile_grid_shape: List[int],
-                outNNZ: int, bias=None, relu: bool = False):
+                outNNZ: int, bias=None, relu: bool = False, master=None):
         ctx.tile_grid_shape = tile_grid_shape
+        ctx.master = master if master is not None else (None, None)
         ctx.tag = profiling.current_tag
         ctx.relu = bool(relu)
         ctx.has_bias = bias is not None
@@ -57,15 +60,23 @@ class ConvFunction(torch.autograd.Function):
         if ctx.relu or ctx.has_bias:    # gradient mask and bias gradient in one pass over the rows
             d_out, d_bias = epilogue_backward(d_out, out, ctx.relu, ctx.has_bias)
             if d_bias is not None:
-                d_bias = d_bias.to(ctx.bias_dtype)
+                if ctx.master[1] is not None:
+                    ctx.master[1].add_(d_bias)
+                    d_bias = None
+                else:
+                    d_bias = d_bias.to(ctx.bias_dtype)
         meta = dict(iC=weight.shape[1], oC=weight.shape[2], n_in=feature.shape[0], n_out=d_out.shape[0],
                     esize=feature.element_size())
         with profiling.section("dgrad:" + ctx.tag, **meta):
             d_feature = rule_conv_d_feature(d_out, weight.permute(0, 2, 1).contiguous(), rules, rule_size,
                                             ctx.tile_grid_shape, feature.shape[0])
         with profiling.section("wgrad:" + ctx.tag, **meta):
-            d_weight = rule_conv_d_weight(feature, d_out, rules, rule_size).to(feature.dtype)
-        return d_feature, d_weight, None, None, None, None, d_bias, None
+            if ctx.master[0] is not None:
+                rule_conv_d_weight(feature, d_out, rules, rule_size, out=ctx.master[0], accumulate=True)
+                d_weight = None
+            else:
+                d_weight = rule_conv_d_weight(feature, d_out, rules, rule_size).to(feature.dtype)
+        return d_feature, d_weight, None, None, None, None, d_bias, None, None
 
 
 class ToDenseFunction(torch.autograd.Function):

@@ -54,6 +54,7 @@ class ScanPipeline:
             slot.dev_in.append(None)
         views = []
         nbytes = 0
+        fresh = False
         for i, h in enumerate(host):
             if not h.is_pinned():
                 raise RuntimeError("ScanPipeline inputs must be pinned host tensors (tensor.pin_memory())")
@@ -61,11 +62,13 @@ class ScanPipeline:
             rows = h.shape[0] if h.dim() > 0 else 1
             if buf is None or buf.dtype != h.dtype or buf.shape[1:] != h.shape[1:] or buf.shape[0] < rows:
                 buf = torch.empty((_grow(rows),) + tuple(h.shape[1:]), dtype=h.dtype, device=self.device)
+                buf.record_stream(self.copy_in)     # written by the copy-in stream: not to be recycled under it
                 slot.dev_in[i] = buf
+                fresh = True
             views.append(buf[:rows] if h.dim() > 0 else buf[0])
             nbytes += h.numel() * h.element_size()
         self.h2d_bytes = nbytes
-        return views
+        return views, fresh
 
     def submit(self, host_inputs: Sequence[torch.Tensor]) -> int:
         """Enqueue copy-in, compute and copy-out of one batch; returns a ticket for ``result``."""
@@ -75,12 +78,15 @@ class ScanPipeline:
             raise RuntimeError("ScanPipeline: fetch result(%d) before submitting batch %d (depth %d)"
                                % (ticket - self.depth, ticket, self.depth))
         compute = torch.cuda.current_stream(self.device)
-        views = self._stage_in(slot, host_inputs)   # (re)allocation happens on the compute stream's pool
+        views, fresh = self._stage_in(slot, host_inputs)   # (re)allocation happens on the compute stream's pool
         with torch.cuda.stream(self.copy_in):
             if slot.used:
                 self.copy_in.wait_event(slot.compute_done)   # the previous batch of this slot has read its inputs
-            else:
-                self.copy_in.wait_stream(compute)            # fresh buffers: order behind their allocation
+            if fresh or not slot.used:
+                # A new staging buffer comes from the compute stream's pool: the block may have just been freed by
+                # work that is still running there (the other batch in flight), so the copy must not start before
+                # everything enqueued on the compute stream so far has finished.
+                self.copy_in.wait_stream(compute)
             for v, h in zip(views, host_inputs):
                 v.copy_(h, non_blocking=True)
             slot.h2d_done.record(self.copy_in)

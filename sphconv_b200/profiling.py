@@ -20,20 +20,46 @@ def is_active():
     return _active
 
 
+_open = []                # stop events of the sections currently open on the current stream (innermost last)
+current_rule_tag = ""     # name of the rule set being generated (set by Conv3d.forward), for side-stream sections
+
+
 @contextlib.contextmanager
-def section(name, **meta):
-    """Times the GPU work enqueued inside the block on the current stream when profiling is enabled."""
+def section(name, stream=None, **meta):
+    """Times the GPU work enqueued inside the block when profiling is enabled: on the current stream, or on
+    `stream` (work a layer puts on a side stream).  A section on the current stream ends where `mark_stop()` was
+    called inside it, else at the end of the block."""
     if not _active:
         yield
         return
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
+    if stream is not None:
+        start.record(stream)
+        try:
+            yield
+        finally:
+            stop.record(stream)
+            _records.append((name, start, stop, meta))
+        return
     start.record()
+    state = [stop, False]
+    _open.append(state)
     try:
         yield
     finally:
-        stop.record()
+        _open.pop()
+        if not state[1]:
+            stop.record()
         _records.append((name, start, stop, meta))
+
+
+def mark_stop():
+    """Ends the innermost open section here (its kernels are enqueued; what follows in the block is a wait on
+    other streams' work that should not count as the section's time)."""
+    if _active and _open and not _open[-1][1]:
+        _open[-1][0].record()
+        _open[-1][1] = True
 
 
 def collect(reset=True):

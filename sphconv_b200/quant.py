@@ -42,7 +42,8 @@ class QuantConv:
         tag = c.name or "{}{}_{}".format("subm" if c.subm else "conv", c.in_channels, c.out_channels)
         datas = x.find_rule(c.indice_key) if c.indice_key is not None else None
         if datas is None:
-            with profiling.section("rules:" + tag, subm=c.subm, n_in=x.feature.shape[0]):
+            profiling.current_rule_tag = tag
+            with profiling.section("rules:" + tag, **c._rule_meta(x, in_shape, out_shape)):
                 datas = c._rules(x, in_shape, out_shape)
             if c.indice_key is not None:
                 x.rule_cache[c.indice_key] = datas

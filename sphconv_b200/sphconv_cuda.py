@@ -74,7 +74,8 @@ def _lists_beside(dev, g, oz_ptr, out_nnz, nbr, tnm, rules, rule_size):
     tables_done = torch.cuda.Event()
     tables_done.record(main)
     side.wait_event(tables_done)
-    with torch.cuda.device(dev):
+    from . import profiling
+    with torch.cuda.device(dev), profiling.section("lists:" + profiling.current_rule_tag, stream=side):
         C.check(C.lib().sph_rule_lists(C.ptr(oz_ptr), ctypes.byref(g), out_nnz, C.ptr(nbr), tnm, C.ptr(rules),
                                        C.ptr(rule_size), int(config.fill_unused_rules), C.ptr(C.status_tensor(dev)),
                                        ctypes.c_void_p(side.cuda_stream)))
@@ -326,6 +327,9 @@ def rule_conv(feature: torch.Tensor, weight: torch.Tensor, rules, ruleSize, outN
     [outNNZ,oC].  Keyword arguments are extensions (fused epilogue relu(acc*scale + bias), output dtype)."""
     tb = _tables_for(rules, ruleSize, feature.shape[0], int(outNNZ), need_t=False)
     out = _gather(feature, weight, tb.nbr, int(outNNZ), False, scale, bias, relu, out_dtype)
+    if getattr(rules, "_sph_ready", None) is not None:
+        from . import profiling
+        profiling.mark_stop()          # a timed section around this call ends with the kernel, not with the join
     _join_lists(rules)
     return out
 
@@ -343,20 +347,30 @@ def rule_conv_d_feature(feature: torch.Tensor, weight: torch.Tensor, rules, rule
     return _gather(feature, weight, tb.nbr, n_in, True, None, None, False, None)
 
 
-def rule_conv_d_weight(feature: torch.Tensor, d_featureOut: torch.Tensor, rules, ruleSize) -> torch.Tensor:
-    """ref: rule_conv_d_weight, src/sphconv/rule_conv.cu:469-518.  Returns float32 [KV,iC,oC]."""
-    C.require_cuda(feature, d_featureOut)
+def rule_conv_d_weight(feature: torch.Tensor, d_featureOut: torch.Tensor, rules, ruleSize, *,
+                       out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """ref: rule_conv_d_weight, src/sphconv/rule_conv.cu:469-518.  Returns float32 [KV,iC,oC].
+    Keyword arguments are extensions: `out` is a caller-owned contiguous float32 [KV,iC,oC] tensor (e.g. a slice
+    of a flat gradient buffer) the kernel writes instead of a fresh one; with `accumulate` it adds to what is there."""
+    C.require_cuda(feature, d_featureOut, out)
     if feature.dtype != d_featureOut.dtype:
         raise RuntimeError("feature and gradient dtypes differ")
     tb = _tables_for(rules, ruleSize, feature.shape[0], d_featureOut.shape[0], need_t=False)
     kv = tb.nbr.shape[0]
     k_ch, n_ch = feature.shape[1], d_featureOut.shape[1]
     dev = feature.device
-    dw = torch.empty((kv, k_ch, n_ch), dtype=torch.float32, device=dev)
+    if out is None:
+        dw = torch.empty((kv, k_ch, n_ch), dtype=torch.float32, device=dev)
+        accumulate = False
+    else:
+        if out.dtype != torch.float32 or out.numel() != kv * k_ch * n_ch:
+            raise RuntimeError("out must be float32 with %d x %d x %d elements" % (kv, k_ch, n_ch))
+        dw = out
     with torch.cuda.device(dev):
         C.check(C.lib().sph_conv_wgrad(C.ptr(feature), C.ptr(d_featureOut), C.DTYPE_CODE[feature.dtype],
                                        feature.shape[0], C.ptr(tb.nbr), d_featureOut.shape[0], kv, k_ch, n_ch,
-                                       C.ptr(dw), 1, C.ptr(C.status_tensor(dev)), C.stream_ptr(dev)))
+                                       C.ptr(dw), 0 if accumulate else 1, C.ptr(C.status_tensor(dev)),
+                                       C.stream_ptr(dev)))
     _join_lists(rules)
     return dw
 
@@ -453,9 +467,8 @@ def epilogue_backward(d_out: torch.Tensor, out: Optional[torch.Tensor], relu: bo
     out = None if out is None else out.contiguous()
     C.require_cuda(d_out, out)
     n, ch = d_out.shape
-    if d_out.dtype not in (torch.float32, torch.float16, torch.bfloat16) or 256 % ch != 0:
-        d_pre = torch.where(out > 0, d_out, torch.zeros((), dtype=d_out.dtype, device=d_out.device)) if relu else d_out
-        return d_pre, (d_pre.sum(0, dtype=torch.float32) if need_bias else None)
+    if d_out.dtype not in (torch.float32, torch.float16, torch.bfloat16) or ch > 256:
+        raise RuntimeError("epilogue_backward: float32 / float16 / bfloat16 gradients with at most 256 channels")
     dev = d_out.device
     d_pre = torch.empty_like(d_out) if relu else None
     d_bias = torch.empty((ch,), dtype=torch.float32, device=dev) if need_bias else None

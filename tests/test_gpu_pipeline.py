@@ -50,6 +50,40 @@ def test_pipeline_matches_direct_calls():
     assert sphconv.check_status() == 0
 
 
+def test_pipeline_slot_regrown_while_other_batch_in_flight():
+    """The second use of a slot needs a staging buffer more than 1.25x larger than its first use: the new buffer comes
+    from the compute stream's pool while the other slot's batch is still computing, and the copy-in must wait for
+    that work.  Results must equal direct calls for every batch."""
+    net = build_encoder8(dtype=torch.float16, device=DEV).eval()
+    sizes = [1, 1, 4, 6, 2, 8]          # scans per batch: slot 0 sees 1 -> 4 -> 2, slot 1 sees 1 -> 6 -> 8
+    batches = [_host_batch(10 * i, B) for i, B in enumerate(sizes)]
+    shape = batches[0][1]
+
+    def run_b(B):
+        def run(f, zi, zp):
+            y = net(sphconv.SparseConvTensor(f, shape, B, z_idx=zi, z_ptr=zp))
+            return {"feature": y.feature, "z_idx": y.z_idx}
+        return run
+
+    with torch.no_grad():
+        direct = [{k: v.cpu().clone() for k, v in run_b(B)(*[t.to(DEV) for t in host]).items()}
+                  for (host, _), B in zip(batches, sizes)]
+        cur = {"B": 1}
+        pipe = sphconv.ScanPipeline(lambda f, zi, zp: run_b(cur["B"])(f, zi, zp), device=DEV, depth=2)
+        tickets, got = [], []
+        for (host, _), B in zip(batches, sizes):
+            cur["B"] = B
+            tickets.append(pipe.submit(host))
+            if len(tickets) > 1:
+                got.append({k: v.clone() for k, v in pipe.result(tickets.pop(0)).items()})
+        got.append({k: v.clone() for k, v in pipe.result(tickets.pop(0)).items()})
+        pipe.drain()
+    for g, d in zip(got, direct):
+        for k in d:
+            assert g[k].shape == d[k].shape and torch.equal(g[k], d[k]), k
+    assert sphconv.check_status() == 0
+
+
 def test_pipeline_misuse_is_reported():
     pipe = sphconv.ScanPipeline(lambda x: {"y": x * 2}, device=DEV, depth=1)
     x = torch.arange(8, dtype=torch.float32).pin_memory()
