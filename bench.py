@@ -381,9 +381,13 @@ def main():
     torch.cuda.set_per_process_memory_fraction(0.8, local_rank)   # stay well inside the device: a dead box helps nobody
     dev = torch.device("cuda", local_rank)
     dist = None
+    numa_cpus = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+        # one process per GPU: keep each rank's pinned host buffers in its GPU's NUMA node
+        from sphconv_b200.pipeline import bind_host_to_device
+        numa_cpus = bind_host_to_device(local_rank)
 
     import sphconv_b200 as sphconv
     from sphconv_b200 import _capi, profiling
@@ -675,6 +679,7 @@ def main():
                 "copy_only_ms": None if copy_ms is None else round(copy_ms, 4),
                 "copy_only_what": "the same H2D + D2H bytes per step through the same pinned buffers with nothing "
                                   "computed, all ranks at once: the floor the host side sets for ms_per_step",
+                "host_binding": None if numa_cpus is None else "rank 0 bound to %d CPUs next to its GPU" % len(numa_cpus),
                 "how": "sphconv_b200.ScanPipeline: copies on two side streams, two batches in flight; "
                        "the region times all steps at once, L2 flushes included"},
         "gpu_launches": int(launches) * args.steps,

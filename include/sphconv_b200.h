@@ -29,7 +29,7 @@ extern "C" {
 
 #define SPH_OK 0
 #define SPH_ERR_INVALID (-1)     /* bad argument (null pointer, non-positive size, inconsistent shapes) */
-#define SPH_ERR_UNSUPPORTED (-2) /* valid request this build does not implement (e.g. dilation != 1) */
+#define SPH_ERR_UNSUPPORTED (-2) /* valid request this build does not implement (e.g. an operand shape) */
 #define SPH_ERR_CUDA (-3)        /* a CUDA runtime call failed; see sph_last_error() */
 #define SPH_ERR_LIMIT (-4)       /* size beyond a documented maximum */
 
@@ -50,6 +50,10 @@ typedef struct sph_geom {
   int32_t stride[3];
   int32_t padding[3];
   int32_t tile[2]; /* output tile (tH, tW); default of the reference is {2,2}, sphconv/conv.py:105 */
+  /* Kernel offset k reads input o*stride - padding + k*dilation.  {1,1,1} is the reference: its kernels ignore the
+   * argument (src/sphconv/rules.cu:40-41) while its out_spatial honours it (sphconv/utils/__init__.py:40-42), so other
+   * values have no reference behaviour; here they give the dilated convolution out_spatial describes.  0 reads as 1. */
+  int32_t dilation[3];
 } sph_geom;
 
 const char* sph_last_error(void);
@@ -59,9 +63,9 @@ int64_t sph_kernel_launches(void);
 
 /* ---- host-side geometry helpers --------------------------------------------------------------- */
 
-/* ref: out_spatial, sphconv/utils/__init__.py:27-44 (dilation fixed to 1). */
+/* ref: out_spatial, sphconv/utils/__init__.py:27-44: floor((i + 2p - d(k-1) - 1)/s + 1); dilation may be null (= 1). */
 int sph_out_spatial(const int32_t in_shape[3], const int32_t ksize[3], const int32_t stride[3],
-                    const int32_t padding[3], int32_t out_shape[3]);
+                    const int32_t padding[3], const int32_t dilation[3], int32_t out_shape[3]);
 
 /* ref: huristic_tile_n_max + getInTileSize, src/sphconv/rules.cu:21-34; bit-identical result. */
 int sph_tile_n_max(const sph_geom* g, int64_t nnz);

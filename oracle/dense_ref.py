@@ -32,23 +32,24 @@ def gather_rows(dense, z_idx, z_ptr, B, shape):
     return dense[torch.as_tensor(b), :, torch.as_tensor(x), torch.as_tensor(y), torch.as_tensor(z)]
 
 
-def occupancy_after_conv(z_idx, z_ptr, B, shape, ksize, stride, padding):
+def occupancy_after_conv(z_idx, z_ptr, B, shape, ksize, stride, padding, dilation=(1, 1, 1)):
     """Output occupancy as test/test_rules.py:14-60 computes it: conv3d of ones != 0."""
     ones = np.ones((np.asarray(z_idx).shape[0], 1), dtype=np.float32)
     dense = densify(ones, z_idx, z_ptr, B, shape)
     w = torch.ones((1, 1, *ksize), dtype=torch.float32)
-    out = torch.nn.functional.conv3d(dense, w, None, tuple(stride), tuple(padding))
+    out = torch.nn.functional.conv3d(dense, w, None, tuple(stride), tuple(padding), tuple(dilation))
     return (out != 0)[:, 0]
 
 
-def dense_conv(feature, weight5, z_idx, z_ptr, B, shape, stride, padding, dtype=torch.float64):
+def dense_conv(feature, weight5, z_idx, z_ptr, B, shape, stride, padding, dtype=torch.float64, dilation=(1, 1, 1)):
     """Dense forward.  weight5 is [k0,k1,k2,iC,oC] (sphconv/conv.py:64-65).  Returns dense [B,oC,o0,o1,o2]."""
     dense = densify(np.asarray(feature), z_idx, z_ptr, B, shape).to(dtype)
     w = torch.as_tensor(np.asarray(weight5)).to(dtype).permute(4, 3, 0, 1, 2).contiguous()
-    return torch.nn.functional.conv3d(dense, w, None, tuple(stride), tuple(padding))
+    return torch.nn.functional.conv3d(dense, w, None, tuple(stride), tuple(padding), tuple(dilation))
 
 
-def dense_conv_grads(feature, weight5, d_out_dense_fn, z_idx, z_ptr, B, shape, stride, padding, dtype=torch.float64):
+def dense_conv_grads(feature, weight5, d_out_dense_fn, z_idx, z_ptr, B, shape, stride, padding, dtype=torch.float64,
+                     dilation=(1, 1, 1)):
     """Forward + autograd through the dense conv (test/test_grad.py:7-36).
     d_out_dense_fn(y_dense) -> upstream gradient tensor of y's shape.
     Returns (y_dense, d_feature_rows [NNZ,iC], d_weight [k0,k1,k2,iC,oC])."""
@@ -58,7 +59,7 @@ def dense_conv_grads(feature, weight5, d_out_dense_fn, z_idx, z_ptr, B, shape, s
     dense = torch.zeros((B, H, W, D, f.shape[1]), dtype=dtype)
     dense = dense.index_put((b, x, y, z), f).permute(0, 4, 1, 2, 3)
     w = torch.as_tensor(np.asarray(weight5)).to(dtype).permute(4, 3, 0, 1, 2).contiguous().requires_grad_(True)
-    yd = torch.nn.functional.conv3d(dense, w, None, tuple(stride), tuple(padding))
+    yd = torch.nn.functional.conv3d(dense, w, None, tuple(stride), tuple(padding), tuple(dilation))
     yd.backward(d_out_dense_fn(yd.detach()))
     return yd.detach(), f.grad, w.grad.permute(2, 3, 4, 1, 0).contiguous()
 

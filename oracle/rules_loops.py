@@ -21,10 +21,10 @@ def linear_tile_idx(tile0, tile1, x, y, tile_grid_w):
     return (x // tile0) * tile_grid_w + (y // tile1)
 
 
-def in_tile_size(out_tile, stride, ksize):
-    """src/sphconv/rules.cu:30-34"""
+def in_tile_size(out_tile, stride, ksize, dilation=1):
+    """src/sphconv/rules.cu:30-34 (dilation = 1 there: a dilated kernel spans dilation * (ksize - 1) + 1 inputs)."""
     assert stride <= ksize
-    return stride * (out_tile - 1) + ksize
+    return stride * (out_tile - 1) + dilation * (ksize - 1) + 1
 
 
 def heuristic_tile_n_max(in_tile_h, in_tile_w, B, H, W, D, nnz):
@@ -46,10 +46,11 @@ def c_div(a, b):
     return -q if (a < 0) != (b < 0) else q
 
 
-def out_coord(k, x, s, pad):
-    """src/sphconv/rules.cu:36-45; dilation is ignored there and here."""
-    if c_rem(x + pad - k, s) == 0:
-        return c_div(x + pad - k, s)
+def out_coord(k, x, s, pad, d=1):
+    """src/sphconv/rules.cu:36-45.  The reference ignores dilation here (d = 1); for d != 1 offset k reads input
+    o*s - pad + k*d, the definition its own out_spatial implies (sphconv/utils/__init__.py:40-42)."""
+    if c_rem(x + pad - k * d, s) == 0:
+        return c_div(x + pad - k * d, s)
     return -1
 
 
@@ -78,26 +79,26 @@ def get_rules_subm(z_idx, z_ptr, B, shape, out_shape, ksize, stride, padding, di
                     grid[b, x, y, zi[pos]] = pos
     KV = KH * KW * KD
     n_tile = div_up(oH, tile[0]) * div_up(oW, tile[1])          # rules.cu:353
-    tnm = heuristic_tile_n_max(in_tile_size(tile[0], stride[0], KH), in_tile_size(tile[1], stride[1], KW),
-                               B, H, W, D, nnz)                 # rules.cu:356-359
+    tnm = heuristic_tile_n_max(in_tile_size(tile[0], stride[0], KH, dilation[0]),
+                               in_tile_size(tile[1], stride[1], KW, dilation[1]), B, H, W, D, nnz)                 # rules.cu:356-359
     rules = np.full((n_tile, KV, 2, tnm), -1, dtype=np.int32)   # rules.cu:364-366
     rule_size = np.zeros((n_tile, KV), dtype=np.int32)          # rules.cu:368-369
     tgw = div_up(oW, tile[1])
     for k in range(KV):                                         # getSubMRulesKernel 234-311
         kh, kw, kd = k // (KW * KD), (k // KD) % KW, k % KD
         for x in range(H):
-            ox = out_coord(kh, x, stride[0], padding[0])
+            ox = out_coord(kh, x, stride[0], padding[0], dilation[0])
             if ox < 0 or ox >= oH:
                 continue
             for y in range(W):
-                oy = out_coord(kw, y, stride[1], padding[1])
+                oy = out_coord(kw, y, stride[1], padding[1], dilation[1])
                 if oy < 0 or oy >= oW:
                     continue
                 t = linear_tile_idx(tile[0], tile[1], ox, oy, tgw)
                 for b in range(B):
                     s, e = _col_range(zp, b, x, y, H, W)
                     for gin in range(s, e):
-                        oz = out_coord(kd, int(zi[gin]), stride[2], padding[2])
+                        oz = out_coord(kd, int(zi[gin]), stride[2], padding[2], dilation[2])
                         if oz < 0 or oz >= oD:
                             continue
                         gout = grid[b, ox, oy, oz]
@@ -124,17 +125,17 @@ def get_rules(z_idx, z_ptr, B, shape, out_shape, ksize, stride, padding, dilatio
     for k in range(KV):                                         # prepareGridKernel 98-150
         kh, kw, kd = k // (KW * KD), (k // KD) % KW, k % KD
         for x in range(H):
-            ox = out_coord(kh, x, stride[0], padding[0])
+            ox = out_coord(kh, x, stride[0], padding[0], dilation[0])
             if ox < 0 or ox >= oH:
                 continue
             for y in range(W):
-                oy = out_coord(kw, y, stride[1], padding[1])
+                oy = out_coord(kw, y, stride[1], padding[1], dilation[1])
                 if oy < 0 or oy >= oW:
                     continue
                 for b in range(B):
                     s, e = _col_range(zp, b, x, y, H, W)
                     for pos in range(s, e):
-                        oz = out_coord(kd, int(zi[pos]), stride[2], padding[2])
+                        oz = out_coord(kd, int(zi[pos]), stride[2], padding[2], dilation[2])
                         if oz < 0 or oz >= oD:
                             continue
                         grid[b, ox, oy, oz] = 1
@@ -144,8 +145,8 @@ def get_rules(z_idx, z_ptr, B, shape, out_shape, ksize, stride, padding, dilatio
     excl[0] = 0
     grid = grid + excl.reshape(B, oH, oW, 1)                    # rules.cu:443 (1-based global out row)
     n_tile = div_up(oH, tile[0]) * div_up(oW, tile[1])
-    tnm = heuristic_tile_n_max(in_tile_size(tile[0], stride[0], KH), in_tile_size(tile[1], stride[1], KW),
-                               B, H, W, D, nnz)
+    tnm = heuristic_tile_n_max(in_tile_size(tile[0], stride[0], KH, dilation[0]),
+                               in_tile_size(tile[1], stride[1], KW, dilation[1]), B, H, W, D, nnz)
     rules = np.full((n_tile, KV, 2, tnm), -1, dtype=np.int32)
     rule_size = np.zeros((n_tile, KV), dtype=np.int32)
     out_nnz = int(oz_ptr.reshape(-1)[-1]) if oz_ptr.size else 0  # rules.cu:461
@@ -154,18 +155,18 @@ def get_rules(z_idx, z_ptr, B, shape, out_shape, ksize, stride, padding, dilatio
     for k in range(KV):                                         # getOzIndicesAndRulesKernel 156-228
         kh, kw, kd = k // (KW * KD), (k // KD) % KW, k % KD
         for x in range(H):
-            ox = out_coord(kh, x, stride[0], padding[0])
+            ox = out_coord(kh, x, stride[0], padding[0], dilation[0])
             if ox < 0 or ox >= oH:
                 continue
             for y in range(W):
-                oy = out_coord(kw, y, stride[1], padding[1])
+                oy = out_coord(kw, y, stride[1], padding[1], dilation[1])
                 if oy < 0 or oy >= oW:
                     continue
                 t = linear_tile_idx(tile[0], tile[1], ox, oy, tgw)
                 for b in range(B):
                     s, e = _col_range(zp, b, x, y, H, W)
                     for gin in range(s, e):
-                        oz = out_coord(kd, int(zi[gin]), stride[2], padding[2])
+                        oz = out_coord(kd, int(zi[gin]), stride[2], padding[2], dilation[2])
                         if oz < 0 or oz >= oD:
                             continue
                         gout = int(grid[b, ox, oy, oz]) - 1

@@ -35,16 +35,19 @@ def row_coords(z_idx, z_ptr, B, H, W):
     return b, x, y, z
 
 
-def _candidates(b, x, y, z, out_shape, ksize, stride, padding):
+def _candidates(b, x, y, z, out_shape, ksize, stride, padding, dilation=(1, 1, 1)):
     """All (input row, k) whose output coordinate is inside the output shape.
-    Yields per offset k: rows (int64 index array), ox, oy, oz."""
+    Yields per offset k: rows (int64 index array), ox, oy, oz.
+    The reference's kernels ignore `dilation` (src/sphconv/rules.cu:36-45) while its Python out_spatial honours it
+    (sphconv/utils/__init__.py:40-42), so it has no consistent behaviour for dilation != 1; here offset k reads input
+    i = o*s - pad + k*d, the definition out_spatial implies (dense conv3d with dilation).  d = 1 is the reference."""
     oH, oW, oD = out_shape
     KH, KW, KD = ksize
     for k in range(KH * KW * KD):
         kh, kw, kd = k // (KW * KD), (k // KD) % KW, k % KD
-        nx = x + padding[0] - kh
-        ny = y + padding[1] - kw
-        nz = z + padding[2] - kd
+        nx = x + padding[0] - kh * dilation[0]
+        ny = y + padding[1] - kw * dilation[1]
+        nz = z + padding[2] - kd * dilation[2]
         ok = (nx >= 0) & (ny >= 0) & (nz >= 0)
         ok &= (nx % stride[0] == 0) & (ny % stride[1] == 0) & (nz % stride[2] == 0)
         ox, oy, oz = nx // stride[0], ny // stride[1], nz // stride[2]
@@ -87,10 +90,10 @@ def get_rules_subm(z_idx, z_ptr, B, shape, out_shape, ksize, stride, padding, di
     KV = ksize[0] * ksize[1] * ksize[2]
     tgw = div_up(oW, tile[1])
     n_tile = div_up(oH, tile[0]) * tgw
-    tnm = heuristic_tile_n_max(in_tile_size(tile[0], stride[0], ksize[0]), in_tile_size(tile[1], stride[1], ksize[1]),
-                               B, H, W, D, z.shape[0])
+    tnm = heuristic_tile_n_max(in_tile_size(tile[0], stride[0], ksize[0], dilation[0]),
+                               in_tile_size(tile[1], stride[1], ksize[1], dilation[1]), B, H, W, D, z.shape[0])
     pairs_k = []
-    for k, rows, ox, oy, oz in _candidates(b, x, y, z, out_shape, ksize, stride, padding):
+    for k, rows, ox, oy, oz in _candidates(b, x, y, z, out_shape, ksize, stride, padding, dilation):
         key = ((b[rows] * oH + ox) * oW + oy) * oD + oz
         pos = np.searchsorted(key_sorted, key)
         pos_c = np.minimum(pos, max(key_sorted.shape[0] - 1, 0))
@@ -112,10 +115,10 @@ def get_rules(z_idx, z_ptr, B, shape, out_shape, ksize, stride, padding, dilatio
     KV = ksize[0] * ksize[1] * ksize[2]
     tgw = div_up(oW, tile[1])
     n_tile = div_up(oH, tile[0]) * tgw
-    tnm = heuristic_tile_n_max(in_tile_size(tile[0], stride[0], ksize[0]), in_tile_size(tile[1], stride[1], ksize[1]),
-                               B, H, W, D, z.shape[0])
+    tnm = heuristic_tile_n_max(in_tile_size(tile[0], stride[0], ksize[0], dilation[0]),
+                               in_tile_size(tile[1], stride[1], ksize[1], dilation[1]), B, H, W, D, z.shape[0])
     cand = []
-    for k, rows, ox, oy, oz in _candidates(b, x, y, z, out_shape, ksize, stride, padding):
+    for k, rows, ox, oy, oz in _candidates(b, x, y, z, out_shape, ksize, stride, padding, dilation):
         key = ((b[rows] * oH + ox) * oW + oy) * oD + oz
         cand.append((rows, ox, oy, key))
     all_keys = np.concatenate([c[3] for c in cand]) if cand else np.zeros(0, np.int64)

@@ -27,7 +27,7 @@ cint = ctypes.c_int
 class Geom(ctypes.Structure):
     """struct sph_geom"""
     _fields_ = [("B", i32), ("in_shape", i32 * 3), ("out_shape", i32 * 3), ("ksize", i32 * 3),
-                ("stride", i32 * 3), ("padding", i32 * 3), ("tile", i32 * 2)]
+                ("stride", i32 * 3), ("padding", i32 * 3), ("tile", i32 * 2), ("dilation", i32 * 3)]
 
 
 class VoxelGrid(ctypes.Structure):
@@ -41,7 +41,7 @@ SIGNATURES = {
     "sph_last_error": (ctypes.c_char_p, []),
     "sph_version": (cint, []),
     "sph_kernel_launches": (i64, []),
-    "sph_out_spatial": (cint, [c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
+    "sph_out_spatial": (cint, [c_i32p, c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
     "sph_tile_n_max": (cint, [ctypes.POINTER(Geom), i64]),
     "sph_num_tiles": (cint, [ctypes.POINTER(Geom)]),
     "sph_rules_subm_scratch_bytes": (i64, [ctypes.POINTER(Geom), i64]),
@@ -98,7 +98,7 @@ def check(rc):
     return rc
 
 
-def make_geom(B, in_shape, out_shape, ksize, stride, padding, tile):
+def make_geom(B, in_shape, out_shape, ksize, stride, padding, tile, dilation=(1, 1, 1)):
     g = Geom()
     g.B = int(B)
     for i in range(3):
@@ -107,6 +107,7 @@ def make_geom(B, in_shape, out_shape, ksize, stride, padding, tile):
         g.ksize[i] = int(ksize[i])
         g.stride[i] = int(stride[i])
         g.padding[i] = int(padding[i])
+        g.dilation[i] = int(dilation[i])
     g.tile[0], g.tile[1] = int(tile[0]), int(tile[1])
     return g
 

@@ -30,6 +30,26 @@ def _stale():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+HOOKS_LIB = os.path.join(LIBDIR, "libsphconv_b200_hooks.so")
+
+
+def build_test_hooks(force=False):
+    """A second library for the test of the bounded waits only: the same sources, with conv_tc.cu compiled with
+    -DSPH_TEST_HOOKS (a 10 ms wait limit and the entry point sph_test_withhold_arrival).  The shipped library holds
+    none of it.  Returns the path."""
+    build(force=force)
+    src = os.path.join(CSRC, "conv_tc.cu")
+    if not force and os.path.exists(HOOKS_LIB) and os.path.getmtime(HOOKS_LIB) >= os.path.getmtime(LIB):
+        return HOOKS_LIB
+    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
+    obj = os.path.join(LIBDIR, "conv_tc_hooks.o")
+    subprocess.check_call([_nvcc(), *flags, "-DSPH_TEST_HOOKS", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c", src,
+                           "-o", obj], stdout=subprocess.DEVNULL, stderr=subprocess.STDOUT)
+    objs = [os.path.join(LIBDIR, s_.replace(".cu", ".o")) for s_ in SOURCES if s_ != "conv_tc.cu"] + [obj]
+    subprocess.check_call([_nvcc(), "-shared", "-o", HOOKS_LIB, *objs, "-lcudart"])
+    return HOOKS_LIB
+
+
 def build(force=False, verbose=False):
     """Compile every .cu into one shared library; returns its path."""
     if not force and not _stale():
@@ -38,7 +58,6 @@ def build(force=False, verbose=False):
     flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
     if verbose:
         flags += ["-Xptxas", "-v"]
-    flags += os.environ.get("SPH_NVCC_EXTRA", "").split()   # developer builds, e.g. -DSPH_TC_PROF
     objs = []
     procs = []
     for src in SOURCES:
@@ -60,3 +79,4 @@ def build(force=False, verbose=False):
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_test_hooks(force="--force" in sys.argv))

@@ -29,44 +29,37 @@ class Convolution(SphModule):
                  padding: List[int], dilation: List[int], groups: int, tile_size: List[int], bias: bool, subm: bool,
                  name: str, indice_key: Optional[str] = None, **kwargs):
         super().__init__(**kwargs)
-        self.in_channels = in_channels
-        self.out_channels = out_channels
-        self.kernel_size = kernel_size
-        self.stride = stride
-        self.padding = padding
-        self.dilation = dilation
-        self.groups = groups
-        self.tile_size = tile_size
-        self.subm = subm
-        self.indice_key = indice_key
-        self.name = name
+        # attribute and parameter names are the reference's (state_dict and user code read them)
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.stride, self.padding, self.dilation = kernel_size, stride, padding, dilation
+        self.groups, self.tile_size, self.subm = groups, tile_size, subm
+        self.indice_key, self.name = indice_key, name
         self.weight = nn.Parameter(torch.empty((*kernel_size, in_channels, out_channels)))
-        if bias:
-            self.bias = nn.Parameter(torch.empty(out_channels))
-        else:
-            self.register_parameter('bias', None)
+        self.register_parameter('bias', nn.Parameter(torch.empty(out_channels)) if bias else None)
         self.reset_parameters()
 
     def reset_parameters(self):
+        """Kaiming-uniform weight with a = sqrt(5) and a bias uniform in +-1/sqrt(fan_in), the fan computed the way the
+        reference's initialiser computes it for the [k0,k1,k2,iC,oC] layout (sphconv/utils/__init__.py:57-124)."""
         kaiming_uniform_(self.weight, a=math.sqrt(5))
         if self.bias is not None:
-            fan_in, _ = _calculate_fan_in_and_fan_out(self.weight)
-            bound = 1 / math.sqrt(fan_in)
-            nn.init.uniform_(self.bias, -bound, bound)
+            fan_in = _calculate_fan_in_and_fan_out(self.weight)[0]
+            nn.init.uniform_(self.bias, -1.0 / math.sqrt(fan_in), 1.0 / math.sqrt(fan_in))
 
     def extra_repr(self):
-        s = '{in_channels}, {out_channels}, kernel_size={kernel_size}, stride={stride}'
-        if self.padding != (0,) * len(self.padding):
-            s += ', padding={padding}'
-        if self.dilation != (1,) * len(self.dilation):
-            s += ', dilation={dilation}'
+        parts = ["{}, {}".format(self.in_channels, self.out_channels), "kernel_size={}".format(self.kernel_size),
+                 "stride={}".format(self.stride)]
+        if any(p != 0 for p in self.padding):
+            parts.append("padding={}".format(self.padding))
+        if any(d != 1 for d in self.dilation):
+            parts.append("dilation={}".format(self.dilation))
         if self.groups != 1:
-            s += ', groups={groups}'
+            parts.append("groups={}".format(self.groups))
         if self.bias is None:
-            s += ', bias=False'
-        if self.subm is True:
-            s += ', subm={subm}'
-        return s.format(**self.__dict__)
+            parts.append("bias=False")
+        if self.subm:
+            parts.append("subm=True")
+        return ", ".join(parts)
 
 
 class Conv3d(Convolution):
@@ -193,4 +186,5 @@ class SubMConv3d(Conv3d):
                  bias=False, subm=False, indice_key=None, **kwargs):
         super().__init__(in_channels, out_channels, kernel_size, subm=True, stride=stride, padding=padding,
                          dilation=dilation, groups=groups, bias=bias, indice_key=indice_key, **kwargs)
-        self.padding = tuple([k // 2 for k in self.kernel_size])
+        # the reference forces k // 2; for a dilated kernel the padding that keeps the geometry is d * (k // 2)
+        self.padding = tuple([d * (k // 2) for k, d in zip(self.kernel_size, self.dilation)])

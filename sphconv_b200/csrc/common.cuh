@@ -62,6 +62,7 @@ struct Geom {
   int B, H, W, D, oH, oW, oD;
   int KH, KW, KD, KV;
   int sH, sW, sD, pH, pW, pD;
+  int dH, dW, dD;   // dilation: kernel offset k reads input o*s - p + k*d
   int tH, tW, tgH, tgW, nTile;
 };
 

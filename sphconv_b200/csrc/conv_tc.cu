@@ -79,6 +79,9 @@ struct TcParams {
   int* status;
   int num_tiles;
   int tbl_off, w_off, stage_off;   // dynamic shared memory layout (byte offsets)
+#ifdef SPH_TEST_HOOKS
+  int test_withhold;               // test build only: one thread never reports its copies of stage 1
+#endif
 };
 
 // 64 accumulator values of one output channel (64 consecutive output rows) -> the output, one element per row.
@@ -337,6 +340,10 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
           }
         }
       }
+#ifdef SPH_TEST_HOOKS
+      // Test build only: the bounded waits and the wind-down are exercised by a stage that never becomes full.
+      if (!(p.test_withhold && f == 1 && wig == 0 && lane == 0))
+#endif
       cp_async_arrive_noinc(full0 + 8u * s);
       ++own_j;
       s += G;
@@ -526,6 +533,10 @@ bool tc_shape_ok(int dtype, int kv, int K, int N) {
   return plan_smem(&p, kv, &bytes);
 }
 
+#ifdef SPH_TEST_HOOKS
+int g_test_withhold = 0;
+#endif
+
 }  // namespace
 
 int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* packed, const int* nbr, int64_t n_out,
@@ -546,6 +557,9 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
   p.scale = scale; p.bias = bias; p.relu = relu;
   p.out = out; p.out_dtype = out_dtype; p.status = status;
   p.num_tiles = (int)div_up64(n_out, kTileRows);
+#ifdef SPH_TEST_HOOKS
+  p.test_withhold = g_test_withhold;
+#endif
   int smem_bytes = 0;
   if (!plan_smem(&p, kv, &smem_bytes)) {
     set_error("conv_gather_tc: operands do not fit in shared memory");
@@ -605,3 +619,9 @@ int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cu
 }
 
 }  // namespace sph
+
+#ifdef SPH_TEST_HOOKS
+// Test build only (a second library beside the shipped one, see sphconv_b200/build.py): makes the next tensor-core
+// convolution launches withhold one arrival, so that a test can watch a bounded wait run out.
+extern "C" void sph_test_withhold_arrival(int on) { sph::g_test_withhold = on; }
+#endif

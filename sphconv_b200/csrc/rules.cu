@@ -179,9 +179,9 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
             out_row = s_vrow[v];
             const int b = s_vb[v];
             const unsigned xy = s_vxy[v];
-            const int ix = (int)(xy >> 16) * g.sH - g.pH + kh;
-            const int iy = (int)(xy & 0xffffu) * g.sW - g.pW + kw;
-            const int iz0 = s_voz[v] * g.sD - g.pD;   // input depth for kd = 0; kd = j reads iz0 + j
+            const int ix = (int)(xy >> 16) * g.sH - g.pH + kh * g.dH;
+            const int iy = (int)(xy & 0xffffu) * g.sW - g.pW + kw * g.dW;
+            const int iz0 = s_voz[v] * g.sD - g.pD;   // input depth for kd = 0; kd = j reads iz0 + j * dD
             if (ix >= 0 && ix < g.H && iy >= 0 && iy < g.W) {
               const int64_t ci = ((int64_t)b * g.H + ix) * g.W + iy;
               if (use_mask) {
@@ -190,7 +190,7 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
                 int cstart = -1;
 #pragma unroll
                 for (int j = 0; j < kMaxKD; ++j) {
-                  const int iz = iz0 + j;
+                  const int iz = iz0 + j * g.dD;
                   if (j < g.KD && iz >= 0 && iz < g.D) {
                     if ((iz >> 5) != cur_w) {
                       cur_w = iz >> 5;
@@ -209,7 +209,7 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
                   const int d = __ldg(in_zi + r) - iz0;
 #pragma unroll
                   for (int j = 0; j < kMaxKD; ++j)
-                    if (d == j && j < g.KD && found[j] < 0) found[j] = r;
+                    if (d == j * g.dD && j < g.KD && found[j] < 0) found[j] = r;
                 }
               }
             }
@@ -286,9 +286,9 @@ nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, G
   int* dst = nbr + r;
   int* dst_t = nbr_t;
   for (int kh = 0; kh < g.KH; ++kh) {
-    const int ix = ox * g.sH - g.pH + kh;
+    const int ix = ox * g.sH - g.pH + kh * g.dH;
     for (int kw = 0; kw < g.KW; ++kw) {
-      const int iy = oy * g.sW - g.pW + kw;
+      const int iy = oy * g.sW - g.pW + kw * g.dW;
       const bool col_ok = ix >= 0 && ix < g.H && iy >= 0 && iy < g.W;
       int cstart = 0;
       const uint2* row = cm.table;
@@ -300,7 +300,7 @@ nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, G
       int cur_w = -1;
       uint2 e = make_uint2(0u, 0u);
       for (int kd = 0; kd < g.KD; ++kd) {
-        const int iz = iz0 + kd;
+        const int iz = iz0 + kd * g.dD;
         int found = -1;
         if (col_ok && iz >= 0 && iz < g.D) {
           if ((iz >> 5) != cur_w) {
@@ -502,7 +502,7 @@ strided_mask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, Geom
       for (int j = 0; j < 8; ++j) m[j] = 0;
       auto add_depth = [&](int z) {
         for (int kd = 0; kd < g.KD; ++kd) {
-          int num = z + g.pD - kd;
+          int num = z + g.pD - kd * g.dD;
           if (num < 0) break;
           if (num % g.sD) continue;
           int oz = num / g.sD;
@@ -516,10 +516,10 @@ strided_mask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, Geom
         }
       };
       for (int kh = 0; kh < g.KH; ++kh) {
-        int ix = ox * g.sH - g.pH + kh;
+        int ix = ox * g.sH - g.pH + kh * g.dH;
         if (ix < 0 || ix >= g.H) continue;
         for (int kw = 0; kw < g.KW; ++kw) {
-          int iy = oy * g.sW - g.pW + kw;
+          int iy = oy * g.sW - g.pW + kw * g.dW;
           if (iy < 0 || iy >= g.W) continue;
           int64_t ci = ((int64_t)b * g.H + ix) * g.W + iy;
           if (use_mask) {
@@ -558,7 +558,7 @@ strided_mask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, Geom
 constexpr int kBitsWords = 8;
 
 __host__ __device__ inline bool strided_bits_ok(const Geom& g) {
-  return (31 * g.sD + g.KD - 1) / 32 + 2 <= kBitsWords;
+  return (31 * g.sD + (g.KD - 1) * g.dD) / 32 + 2 <= kBitsWords;
 }
 
 __global__ void __launch_bounds__(256)
@@ -574,7 +574,7 @@ strided_bits_kernel(Geom g, int words_out, int64_t ncols_out, ColMask cm, uint32
   const int oz_lo = w * 32;
   const int n_bits = min(g.oD - oz_lo, 32);
   const int iz_lo = max(0, oz_lo * g.sD - g.pD);
-  const int iz_hi = min(g.D - 1, (oz_lo + n_bits - 1) * g.sD - g.pD + g.KD - 1);
+  const int iz_hi = min(g.D - 1, (oz_lo + n_bits - 1) * g.sD - g.pD + (g.KD - 1) * g.dD);
   uint32_t out = 0;
   if (iz_lo <= iz_hi) {
     const int w_lo = iz_lo >> 5;
@@ -583,10 +583,10 @@ strided_bits_kernel(Geom g, int words_out, int64_t ncols_out, ColMask cm, uint32
 #pragma unroll
     for (int j = 0; j < kBitsWords; ++j) u[j] = 0u;
     for (int kh = 0; kh < g.KH; ++kh) {
-      const int ix = ox * g.sH - g.pH + kh;
+      const int ix = ox * g.sH - g.pH + kh * g.dH;
       if (ix < 0 || ix >= g.H) continue;
       for (int kw = 0; kw < g.KW; ++kw) {
-        const int iy = oy * g.sW - g.pW + kw;
+        const int iy = oy * g.sW - g.pW + kw * g.dW;
         if (iy < 0 || iy >= g.W) continue;
         const uint2* row = cm.table + (((int64_t)b * g.H + ix) * g.W + iy) * cm.words + w_lo;
 #pragma unroll
@@ -598,7 +598,7 @@ strided_bits_kernel(Geom g, int words_out, int64_t ncols_out, ColMask cm, uint32
       const int base = (oz_lo + bit) * g.sD - g.pD;
       uint32_t hit = 0u;
       for (int kd = 0; kd < g.KD; ++kd) {
-        const int iz = base + kd;
+        const int iz = base + kd * g.dD;
         if (iz >= 0 && iz < g.D) {
           const int wi = (iz >> 5) - w_lo;
           uint32_t word = 0u;
@@ -814,12 +814,16 @@ int make_geom(const sph_geom* s, Geom* o) {
   g.sH = s->stride[0]; g.sW = s->stride[1]; g.sD = s->stride[2];
   g.pH = s->padding[0]; g.pW = s->padding[1]; g.pD = s->padding[2];
   g.tH = s->tile[0]; g.tW = s->tile[1];
+  g.dH = s->dilation[0] ? s->dilation[0] : 1;
+  g.dW = s->dilation[1] ? s->dilation[1] : 1;
+  g.dD = s->dilation[2] ? s->dilation[2] : 1;
   SPH_CHECK_ARG(g.B > 0 && g.H > 0 && g.W > 0 && g.D > 0, "batch and input shape must be positive");
   SPH_CHECK_ARG(g.oH > 0 && g.oW > 0 && g.oD > 0, "output shape must be positive");
   SPH_CHECK_ARG(g.KH > 0 && g.KW > 0 && g.KD > 0, "kernel size must be positive");
   SPH_CHECK_ARG(g.sH > 0 && g.sW > 0 && g.sD > 0, "stride must be positive");
   SPH_CHECK_ARG(g.pH >= 0 && g.pW >= 0 && g.pD >= 0, "padding must be non-negative");
   SPH_CHECK_ARG(g.tH > 0 && g.tW > 0, "tile size must be positive");
+  SPH_CHECK_ARG(g.dH > 0 && g.dW > 0 && g.dD > 0, "dilation must be positive");
   g.KV = g.KH * g.KW * g.KD;
   if (g.KV > kMaxKV) {
     set_error("kernel volume %d exceeds the maximum %d", g.KV, kMaxKV);
@@ -849,12 +853,13 @@ int make_geom(const sph_geom* s, Geom* o) {
 using namespace sph;
 
 extern "C" int sph_out_spatial(const int32_t in_shape[3], const int32_t ksize[3], const int32_t stride[3],
-                               const int32_t padding[3], int32_t out_shape[3]) {
+                               const int32_t padding[3], const int32_t dilation[3], int32_t out_shape[3]) {
   SPH_CHECK_ARG(in_shape && ksize && stride && padding && out_shape, "null argument");
   for (int d = 0; d < 3; ++d) {
-    SPH_CHECK_ARG(stride[d] > 0 && ksize[d] > 0, "stride and kernel size must be positive");
-    // floor((i + 2p - (k-1) - 1)/s + 1) as the reference computes it in floating point
-    int num = in_shape[d] + 2 * padding[d] - (ksize[d] - 1) - 1;
+    const int dil = dilation && dilation[d] ? dilation[d] : 1;
+    SPH_CHECK_ARG(stride[d] > 0 && ksize[d] > 0 && dil > 0, "stride, kernel size and dilation must be positive");
+    // floor((i + 2p - d(k-1) - 1)/s + 1) as the reference computes it in floating point
+    int num = in_shape[d] + 2 * padding[d] - dil * (ksize[d] - 1) - 1;
     int q = num >= 0 ? num / stride[d] : -((-num + stride[d] - 1) / stride[d]);
     out_shape[d] = q + 1;
   }
@@ -872,8 +877,8 @@ extern "C" int sph_tile_n_max(const sph_geom* s, int64_t nnz) {
   int rc = make_geom(s, &g);
   if (rc != SPH_OK) return rc;
   SPH_CHECK_ARG(g.sH <= g.KH && g.sW <= g.KW, "stride larger than the kernel");
-  int in_th = g.sH * (g.tH - 1) + g.KH;
-  int in_tw = g.sW * (g.tW - 1) + g.KW;
+  int in_th = g.sH * (g.tH - 1) + g.dH * (g.KH - 1) + 1;   // = s(t-1) + K of the reference when the dilation is 1
+  int in_tw = g.sW * (g.tW - 1) + g.dW * (g.KW - 1) + 1;
   // same expression, evaluation order and types as the reference: the int product is formed first,
   // then multiplied by the double sparsity, then by 2
   double sparsity = (double)nnz / (double)((int64_t)g.B * g.H * g.W * g.D);

@@ -59,7 +59,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+#ifdef SPH_TEST_HOOKS
+constexpr long long kWaitLimitCycles = 20ll * 1000ll * 1000ll;   // test build: ~10 ms, so that a withheld arrival is noticed at once
+#else
 constexpr long long kWaitLimitCycles = 400ll * 1000ll * 1000ll;  // ~0.2 s of SM clocks: far beyond any healthy wait
+#endif
 
 // Bounded wait.  `abort_flag` is a CTA-shared int: once any thread has timed out every later wait
 // returns at once.  Returns true when the phase completed.  The common case never reads a clock:

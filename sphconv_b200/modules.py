@@ -1,5 +1,4 @@
 """Module containers (ref: sphconv/modules.py)."""
-import sys
 from collections import OrderedDict
 
 import torch
@@ -28,35 +27,29 @@ class Sequential(SphModule):
 
     def __init__(self, *args, **kwargs):
         super().__init__()
-        if len(args) == 1 and isinstance(args[0], OrderedDict):
-            for key, module in args[0].items():
-                self.add_module(key, module)
-        else:
-            for idx, module in enumerate(args):
-                self.add_module(str(idx), module)
-        for name, module in kwargs.items():
-            if sys.version_info < (3, 6):
-                raise ValueError("kwargs only supported in py36+")
+        # accepted forms, as torch.nn.Sequential plus named keyword modules: Sequential(m0, m1, ...),
+        # Sequential(OrderedDict(name=module, ...)), Sequential(m0, name=module, ...)
+        named = list(args[0].items()) if len(args) == 1 and isinstance(args[0], OrderedDict) \
+            else [(str(i), m) for i, m in enumerate(args)]
+        for name, module in named + list(kwargs.items()):
             if name in self._modules:
-                raise ValueError("name exists.")
+                raise ValueError("module name '{}' given twice".format(name))
             self.add_module(name, module)
-        self._sparity_dict = {}
-
-    def __getitem__(self, idx):
-        if not (-len(self) <= idx < len(self)):
-            raise IndexError('index {} is out of range'.format(idx))
-        if idx < 0:
-            idx += len(self)
-        return list(self._modules.values())[idx]
 
     def __len__(self):
         return len(self._modules)
 
+    def __getitem__(self, idx):
+        n = len(self)
+        if not -n <= idx < n:
+            raise IndexError("index {} is out of range".format(idx))
+        return list(self._modules.values())[idx % n]
+
     def add(self, module, name=None):
-        if name is None:
-            name = str(len(self._modules))
-            if name in self._modules:
-                raise KeyError("name exists")
+        """Appends a module under `name` (default: its position)."""
+        name = str(len(self._modules)) if name is None else name
+        if name in self._modules:
+            raise KeyError("module name '{}' exists".format(name))
         self.add_module(name, module)
 
     def forward(self, input):

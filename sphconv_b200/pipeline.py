@@ -29,6 +29,32 @@ class _Slot:
         self.used = False
 
 
+def bind_host_to_device(device_index: int):
+    """Restricts this process to the CPUs that sit next to GPU `device_index` (NVML's CPU affinity of the device), so
+    that the pinned host buffers allocated afterwards land in that GPU's NUMA node: with one process per GPU on a
+    two-socket host, results copied out by eight GPUs otherwise all pour into the memory of whichever node the
+    processes happened to start on.  Call it once, before the first pin_memory().  Returns the CPU list it bound to, or
+    None when NVML / the affinity call is unavailable (nothing is changed then)."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        if not uuid.startswith("GPU-"):
+            uuid = "GPU-" + uuid
+        handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if isinstance(uuid, str) else uuid)
+        n_cpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (n_cpu + 63) // 64)
+        cpus = [i for i in range(n_cpu) if (int(words[i // 64]) >> (i % 64)) & 1]
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:
+        return None
+
+
 def _grow(n):
     return int(n * 1.25) + 16
 

@@ -6,7 +6,10 @@ Differences a caller can see, all documented:
   * pairs inside one (tile,k) list come in a deterministic order (the reference's is atomics order);
   * entries of ``rules`` past ``rule_size`` are -1 only when ``config.fill_unused_rules`` is set
     (no consumer reads them, ``include/sphconv/iterator.cu.h:173-177``);
-  * errors raise ``RuntimeError`` instead of ``printf``/``exit``.
+  * errors raise ``RuntimeError`` instead of ``printf``/``exit``;
+  * ``dilation`` is honoured: kernel offset k reads input o*stride - padding + k*dilation.  The reference's kernels
+    ignore the argument (src/sphconv/rules.cu:40-41) while its ``out_spatial`` sizes the output for a dilated kernel
+    (sphconv/utils/__init__.py:40-42); dilation 1, the only value its tests use, behaves identically.
 
 ``get_rules*`` attach the neighbour tables the convolution kernels read to the returned ``rules``
 tensor (attribute ``_sph``).  Rules without it - cloned, loaded from disk, made elsewhere - are
@@ -48,9 +51,8 @@ def _check_common(zIndices, zPtr, dilation):
     C.require_cuda(zIndices, zPtr)
     if zIndices.dtype != torch.int32 or zPtr.dtype != torch.int32:
         raise RuntimeError("z_idx and z_ptr must be int32")
-    if any(int(d) != 1 for d in dilation):
-        # the reference accepts the argument and ignores it (src/sphconv/rules.cu:40-41)
-        raise RuntimeError("dilation != 1 is not supported")
+    if any(int(d) < 1 for d in dilation):
+        raise RuntimeError("dilation must be positive")
 
 
 _side_streams = {}
@@ -124,7 +126,7 @@ def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, s
     lib = C.lib()
     dev = zIndices.device
     nnz = zIndices.shape[0]
-    g = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    g = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize, dilation)
     kv = int(kernelSize[0]) * int(kernelSize[1]) * int(kernelSize[2])
     n_tile = C.check(lib.sph_num_tiles(ctypes.byref(g)))
     rules = rule_size = None
@@ -146,8 +148,8 @@ def get_rules_subm(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, s
         _lists_beside(dev, g, zPtr, nnz, nbr, tnm, rules, rule_size)
     if exact:
         rules, rule_size = _exact_lists(dev, g, zPtr, nnz, nbr, n_tile, kv)
-    symmetric = all(int(k) % 2 == 1 and int(p) == int(k) // 2 and int(s) == 1
-                    for k, p, s in zip(kernelSize, padding, stride))
+    symmetric = all(int(k) % 2 == 1 and int(p) == int(d) * (int(k) // 2) and int(s) == 1
+                    for k, p, s, d in zip(kernelSize, padding, stride, dilation))
     tables = _Tables(nbr, None, nnz, nnz, rules._version if rules is not None else 0, symmetric)
     if rules is not None:
         rules._sph = tables
@@ -164,9 +166,9 @@ class PendingRules:
         return self.z_idx is zIndices and self.z_ptr is zPtr and self.key == key
 
 
-def _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize):
+def _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize, dilation=(1, 1, 1)):
     return (int(batchSize),) + tuple(int(v) for seq in (spatialShape, outSpatialShape, kernelSize, stride, padding,
-                                                        tileSize) for v in seq)
+                                                        tileSize, dilation) for v in seq)
 
 
 def get_rules_begin(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatialShape: List[int],
@@ -180,8 +182,8 @@ def get_rules_begin(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, 
     nnz = zIndices.shape[0]
     p = PendingRules()
     p.z_idx, p.z_ptr = zIndices, zPtr
-    p.key = _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
-    p.geom = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    p.key = _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize, dilation)
+    p.geom = C.make_geom(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize, dilation)
     scratch_bytes = C.check(lib.sph_rules_strided_scratch_bytes(ctypes.byref(p.geom), nnz))
     p.scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=dev)
     p.oz_ptr = torch.empty((batchSize, int(outSpatialShape[0]), int(outSpatialShape[1])), dtype=torch.int32, device=dev)
@@ -204,7 +206,7 @@ def get_rules(zIndices: torch.Tensor, zPtr: torch.Tensor, batchSize: int, spatia
     """ref: get_rules, src/sphconv/rules.cu:405-486.  Returns [ozIndices, ozPtr, rules, ruleSize].
     `pending` (extension): the result of get_rules_begin on the same arguments; step 1 is then not run again.
     `defer_lists` (extension): as for get_rules_subm."""
-    key = _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize)
+    key = _geom_key(batchSize, spatialShape, outSpatialShape, kernelSize, stride, padding, tileSize, dilation)
     if pending is None or not pending.matches(zIndices, zPtr, key):
         pending = get_rules_begin(zIndices, zPtr, batchSize, spatialShape, outSpatialShape, kernelSize, stride,
                                   padding, dilation, tileSize)

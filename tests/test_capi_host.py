@@ -40,18 +40,22 @@ def test_out_spatial_and_tile_n_max_match_oracle(lib):
         st = np.minimum(rng.integers(1, 3, size=3), ks)
         pd = rng.integers(0, 2, size=3)
         out = arr([0, 0, 0])
-        assert lib.sph_out_spatial(arr(shape), arr(ks), arr(st), arr(pd), out) == 0
+        assert lib.sph_out_spatial(arr(shape), arr(ks), arr(st), arr(pd), None, out) == 0
         want = rules_np.out_spatial(list(shape), list(ks), list(st), list(pd))
+        assert list(out) == want
+        dl = rng.integers(1, 4, size=3) if _ % 2 else np.ones(3, dtype=np.int64)   # every other case dilated
+        assert lib.sph_out_spatial(arr(shape), arr(ks), arr(st), arr(pd), arr(dl), out) == 0
+        want = rules_np.out_spatial(list(shape), list(ks), list(st), list(pd), list(dl))
         assert list(out) == want
         if min(want) < 1:
             continue
         B = int(rng.integers(1, 9))
         tile = rng.integers(1, 5, size=2)
         nnz = int(rng.integers(0, B * int(np.prod(shape)) + 1))
-        g = C.make_geom(B, shape, want, ks, st, pd, tile)
+        g = C.make_geom(B, shape, want, ks, st, pd, tile, dl)
         got = lib.sph_tile_n_max(ctypes.byref(g), nnz)
-        ref = rules_loops.heuristic_tile_n_max(rules_loops.in_tile_size(int(tile[0]), int(st[0]), int(ks[0])),
-                                               rules_loops.in_tile_size(int(tile[1]), int(st[1]), int(ks[1])),
+        ref = rules_loops.heuristic_tile_n_max(rules_loops.in_tile_size(int(tile[0]), int(st[0]), int(ks[0]), int(dl[0])),
+                                               rules_loops.in_tile_size(int(tile[1]), int(st[1]), int(ks[1]), int(dl[1])),
                                                B, int(shape[0]), int(shape[1]), int(shape[2]), nnz)
         assert got == ref
         assert lib.sph_num_tiles(ctypes.byref(g)) == rules_loops.div_up(want[0], int(tile[0])) * rules_loops.div_up(want[1], int(tile[1]))

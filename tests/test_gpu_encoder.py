@@ -87,6 +87,45 @@ def test_encoder_training_step_vs_dense_autograd(dtype, tol):
     assert sphconv.check_status() == 0
 
 
+def test_master_gradient_buffer_keeps_fp32_weight_gradients():
+    """bf16 training with a sharding.GradBuffer attached: the wgrad kernels accumulate into the flat fp32 buffer (no
+    `.grad` comes through autograd, nothing is rounded to bf16), two backward passes add up, and the buffer equals the
+    fp32 result of the op called directly on the same operands."""
+    from sphconv_b200 import sharding
+    b = _batch(1)
+    net = build_encoder8(dtype=torch.bfloat16, device=DEV).train()
+    gb = sharding.GradBuffer(net.parameters())
+    caught = []
+    import sphconv_b200.functional as F
+    orig = F.rule_conv_d_weight
+
+    def spy(feature, d_out, rules, rule_size, **kw):
+        caught.append(orig(feature, d_out, rules, rule_size))      # the same operands, into a fresh fp32 tensor
+        return orig(feature, d_out, rules, rule_size, **kw)
+    F.rule_conv_d_weight = spy
+    try:
+        for rep in range(2):
+            x = _tensor(b, torch.bfloat16, requires_grad=True)
+            y = net(x)
+            g = torch.as_tensor(np.random.default_rng(1).standard_normal(tuple(y.feature.shape)), device=DEV).bfloat16()
+            y.feature.backward(g)
+    finally:
+        F.rule_conv_d_weight = orig
+    mods = list(net._modules.values())
+    assert all(m.weight.grad is None and m.bias.grad is None for m in mods)
+    assert len(caught) == 16
+    for li, m in enumerate(mods):               # backward visits the layers last to first
+        direct = caught[len(mods) - 1 - li] + caught[2 * len(mods) - 1 - li]
+        got = m.weight._sph_master_grad.view(27, m.in_channels, m.out_channels)
+        assert got.dtype == torch.float32
+        assert _rel_l2(got, direct) <= 1e-5, li
+        assert float(m.bias._sph_master_grad.abs().sum()) > 0
+    gb.to_grads()
+    assert all(m.weight.grad.dtype == torch.bfloat16 for m in mods)
+    gb.detach()
+    assert sphconv.check_status() == 0
+
+
 def test_int8_encoder_vs_fp32():
     b = _batch()
     net32 = build_encoder8(dtype=torch.float32, device=DEV).eval()

@@ -210,7 +210,7 @@ def test_deterministic_and_foreign_rules():
 def test_bad_arguments_raise():
     zi, zp = to_dev(np.zeros(0, np.int32), np.zeros((1, 4, 4), np.int32))
     with pytest.raises(RuntimeError):
-        ops.get_rules(zi, zp, 1, [4, 4, 4], [2, 2, 2], [3, 3, 3], [2, 2, 2], [1, 1, 1], [2, 2, 2], [2, 2])   # dilation
+        ops.get_rules(zi, zp, 1, [4, 4, 4], [2, 2, 2], [3, 3, 3], [2, 2, 2], [1, 1, 1], [0, 1, 1], [2, 2])   # dilation 0
     with pytest.raises(RuntimeError):
         ops.get_rules_subm(zi, zp, 1, [4, 4, 4], [2, 2, 2], [3, 3, 3], [1, 1, 1], [1, 1, 1], [1, 1, 1], [2, 2])  # shape
     with pytest.raises(RuntimeError):

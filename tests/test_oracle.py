@@ -112,6 +112,46 @@ def test_subm_conv_vs_masked_dense(ks):
     assert np.allclose(out, want, atol=1e-10)
 
 
+@pytest.mark.parametrize("ks,st,pd,dl", [([3, 3, 3], [1, 1, 1], [2, 2, 2], [2, 2, 2]), ([3, 3, 3], [2, 2, 2], [2, 1, 3], [2, 1, 3]),
+                                         ([2, 3, 2], [1, 2, 1], [1, 2, 0], [3, 2, 1])])
+def test_dilated_conv_vs_dense(ks, st, pd, dl):
+    """Dilation != 1: offset k reads input o*s - pad + k*d (the reference has no consistent behaviour to copy: its
+    kernels ignore the argument, its out_spatial honours it).  Pinned here against dense conv3d with the same
+    dilation: output shape, occupancy, forward, dgrad, wgrad; and loops == numpy."""
+    rng = np.random.default_rng(17)
+    B, shape = 2, [7, 6, 9]
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.3)
+    osh = rules_np.out_spatial(shape, ks, st, pd, dl)
+    oz_idx, oz_ptr, rules, rule_size = rules_loops.get_rules(z_idx, z_ptr, B, shape, osh, ks, st, pd, dl, [2, 2])
+    res = rules_np.get_rules(z_idx, z_ptr, B, shape, osh, ks, st, pd, dl, [2, 2])
+    assert (oz_idx == res["oz_idx"]).all() and (oz_ptr == res["oz_ptr"]).all() and (rule_size == res["rule_size"]).all()
+    assert (rules_np.canonical_pairs(rules, rule_size) == rules_np.canonical_from_table(res)).all()
+    occ = dense_ref.occupancy_after_conv(z_idx, z_ptr, B, shape, ks, st, pd, dl)
+    assert list(occ.shape[1:]) == osh
+    mine = dense_ref.densify(np.ones((oz_idx.shape[0], 1), np.float32), oz_idx, oz_ptr, B, osh)[:, 0] != 0
+    assert (occ == mine).all()
+    iC, oC = 3, 4
+    pairs = rules_np.canonical_from_table(res)
+    feat = rng.standard_normal((z_idx.shape[0], iC))
+    w5 = rng.standard_normal((*ks, iC, oC))
+    out = conv_np.conv_forward(feat, w5.reshape(-1, iC, oC), pairs, res["oz_idx"].shape[0])
+    up = torch.as_tensor(rng.standard_normal((B, oC, *osh)))
+    yd, dfeat, dw5 = dense_ref.dense_conv_grads(feat, w5, lambda y: up, z_idx, z_ptr, B, shape, st, pd, dilation=dl)
+    assert torch.allclose(dense_ref.densify(out, res["oz_idx"], res["oz_ptr"], B, osh), yd, atol=1e-10)
+    d_out = dense_ref.gather_rows(up, res["oz_idx"], res["oz_ptr"], B, osh).numpy()
+    assert np.allclose(conv_np.conv_dgrad(d_out, w5.reshape(-1, iC, oC), pairs, z_idx.shape[0]), dfeat.numpy(), atol=1e-10)
+    assert np.allclose(conv_np.conv_wgrad(feat, d_out, pairs, int(np.prod(ks))).reshape(*ks, iC, oC), dw5.numpy(), atol=1e-10)
+    if st == [1, 1, 1] and all(p == d * (k // 2) for p, d, k in zip(pd, dl, ks)):
+        # submanifold with the "same" padding of a dilated kernel: d * (k // 2)
+        rs = rules_np.get_rules_subm(z_idx, z_ptr, B, shape, shape, ks, st, pd, dl, [2, 2], padded=False)
+        _, _, rl, rsz = rules_loops.get_rules_subm(z_idx, z_ptr, B, shape, shape, ks, st, pd, dl, [2, 2])
+        assert (rules_np.canonical_pairs(rl, rsz) == rules_np.canonical_from_table(rs)).all()
+        o2 = conv_np.conv_forward(feat, w5.reshape(-1, iC, oC), rules_np.canonical_from_table(rs), z_idx.shape[0])
+        want = dense_ref.gather_rows(dense_ref.dense_conv(feat, w5, z_idx, z_ptr, B, shape, st, pd, dilation=dl),
+                                     z_idx, z_ptr, B, shape).numpy()
+        assert np.allclose(o2, want, atol=1e-10)
+
+
 def test_synthetic_configs_are_wellformed():
     for name in ["cfg1", "cfg2", "cfg3"]:
         cfg = synthetic.CONFIGS[name]

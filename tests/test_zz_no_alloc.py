@@ -59,6 +59,36 @@ def test_static_scratch_entry_point_matches_twice_in_a_row():
     _run(lib, fn, a[0], a[1], 2, [8, 12, 64])
 
 
+def test_static_scratch_entry_point_allocates_nothing():
+    """Free device memory as the driver reports it is the same before and after a series of calls (outputs are
+    allocated beforehand; the first call, which looks up the array's address, has already happened)."""
+    lib = C.lib()
+    rng = np.random.default_rng(7)
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, 2, [8, 12, 64], 0.30)
+    zi = torch.as_tensor(z_idx, dtype=torch.int32, device=DEV)
+    zp = torch.as_tensor(z_ptr, dtype=torch.int32, device=DEV)
+    nnz = zi.shape[0]
+    g = C.make_geom(2, [8, 12, 64], [8, 12, 64], [3, 3, 3], [1, 1, 1], [1, 1, 1], [2, 2])
+    n_tile = C.check(lib.sph_num_tiles(ctypes.byref(g)))
+    tnm = C.check(lib.sph_tile_n_max(ctypes.byref(g), nnz))
+    rules = torch.empty((n_tile, 27, 2, tnm), dtype=torch.int32, device=DEV)
+    rule_size = torch.empty((n_tile, 27), dtype=torch.int32, device=DEV)
+    nbr = torch.empty((27, nnz), dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    st = C.stream_ptr(torch.device(DEV))
+    call = lambda: C.check(lib.sph_rules_subm_static(C.ptr(zi), C.ptr(zp), nnz, ctypes.byref(g), tnm, C.ptr(rules),
+                                                     C.ptr(rule_size), C.ptr(nbr), 1, C.ptr(status), st))
+    call()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        call()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    assert int(status.item()) == 0
+
+
 def test_static_scratch_entry_point_rejects_oversized_inputs():
     lib = C.lib()
     # 64 x 2048 x 2048 columns x 8 words x 8 bytes of index is far beyond the built-in 8 MiB
