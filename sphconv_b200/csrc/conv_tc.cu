@@ -43,7 +43,7 @@ constexpr int kTileRows = 256;      // output rows per tile = UMMA N
 #endif
 constexpr int kProducerWarps = SPH_TC_PRODUCER_WARPS;    // gather warps
 #ifndef SPH_GK4
-#define SPH_GK4 3                   // kernel offsets per pipeline stage for 64-byte rows
+#define SPH_GK4 2                   // kernel offsets per pipeline stage for 64-byte rows
 #endif
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kTcThreads = (kProducerWarps + 1 + 4) * 32;
@@ -228,23 +228,30 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
       if (d < 0) d += G;
       return base + d;
     };
+    // Entry e of a lane is compile-time (owned stage os, offset g of the stage, 32-row chunk h): only the row inside
+    // the chunk depends on the lane, so a tile's loads cost a few instructions each (this runs on the gather warps'
+    // own instruction streams, between two stages).
+    constexpr int CH = RPW / 32;                   // 32-slot chunks of the warp's rows
+    int64_t rofs[CH];                              // slot -> row: lane group q keeps its RPL slots together (vector
+#pragma unroll                                     // reads of the parked table), its j-th slot is row q + j * NG
+    for (int h = 0; h < CH; ++h) {
+      const int slot = h * 32 + lane;
+      rofs[h] = wig * RPW + (slot % RPL) * NG + slot / RPL;
+    }
     auto load_tile = [&](int ti) {
-      const int f0 = first_owned(ti);
-      const int f_end = (ti + 1) * groups;
-      const int64_t r0 = ((int64_t)blockIdx.x + (int64_t)ti * gridDim.x) * kTileRows + wig * RPW;
+      const int sj0 = first_owned(ti) - ti * groups;           // first owned stage inside the tile
+      const int64_t r0 = ((int64_t)blockIdx.x + (int64_t)ti * gridDim.x) * kTileRows;
+      bool row_ok[CH];
+#pragma unroll
+      for (int h = 0; h < CH; ++h) row_ok[h] = ti < my_tiles && r0 + rofs[h] < p.n_out;
 #pragma unroll
       for (int e = 0; e < kMaxEnt; ++e) {
-        const int idx = e * 32 + lane;
-        const int f = f0 + (idx / eps) * G;
-        const int rem = idx % eps;
-        const int k = (f - ti * groups) * GK + rem / RPW;
-        // slot -> row: lane group q keeps its RPL slots together (vector reads of the parked table), and its j-th slot
-        // is row q + j * NG of the warp's rows, so that one gather instruction covers NG consecutive rows
-        const int slot = rem & (RPW - 1);
-        const int64_t r = r0 + (slot % RPL) * NG + slot / RPL;
+        constexpr int per_stage = GK * CH;
+        const int os = e / per_stage, g = (e / CH) % GK, h = e % CH;   // compile-time after unrolling
+        const int k = (sj0 + os * G) * GK + g;
+        const int* plane = p.nbr + (int64_t)(p.flip_k ? p.kv - 1 - k : k) * p.n_out + r0;
         // plain loads with no dependent work here: all 32 stay in flight; they are checked when parked
-        ent[e] = (ti < my_tiles && f < f_end && k < p.kv && r < p.n_out)
-                     ? __ldg(p.nbr + (int64_t)(p.flip_k ? p.kv - 1 - k : k) * p.n_out + r) : -1;
+        ent[e] = (row_ok[h] && k < p.kv) ? __ldg(plane + rofs[h]) : -1;
       }
     };
     auto park_tile = [&]() {

@@ -59,32 +59,37 @@ __device__ __forceinline__ int find_row(const int* __restrict__ zi, const int* _
   return -1;
 }
 
-// One thread per input column: set the depth bits, then the running popcount.  The table must be zeroed.
-// row_col (optional) receives the column id of every row.
+// One thread per (input column, 32-bin word): the thread walks the column's rows (a handful; the threads of one
+// column read the same addresses, one transaction per warp), keeps the bits of its word and the number of rows below
+// its word, and writes its {bits, prefix} entry: every entry of the table is written exactly once, coalesced, so the
+// table needs no clearing beforehand.  The thread of word 0 also checks the depth order and parks the column id of
+// every row in row_col (optional).
 __global__ void __launch_bounds__(256)
 build_colmask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, int64_t ncols, int words, int D,
                      uint2* __restrict__ table, int* __restrict__ unsorted, int* __restrict__ row_col) {
-  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= ncols) return;
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= ncols * words) return;
+  const int64_t c = t / words;
+  const int w = (int)(t - c * words);
   const int s = col_start(zp, c), e = __ldg(zp + c);
-  if (e <= s) return;
-  uint2* row = table + c * words;
-  int prev = -1;
+  uint32_t bits = 0u;
+  int below = 0, prev = -1;
   bool bad = false;
   for (int r = s; r < e; ++r) {
-    int z = __ldg(zi + r);
-    if (z <= prev || z >= D) bad = true;
-    prev = z;
-    if (z >= 0 && z < D) row[z >> 5].x |= 1u << (z & 31);
-    if (row_col) row_col[r] = (int)c;
+    const int z = __ldg(zi + r);
+    if (w == 0) {
+      if (z <= prev || z >= D) bad = true;
+      prev = z;
+      if (row_col) row_col[r] = (int)c;
+    }
+    if (z >= 0 && z < D) {
+      const int zw = z >> 5;
+      if (zw == w) bits |= 1u << (z & 31);
+      else if (zw < w) ++below;
+    }
   }
   if (bad) *unsorted = 1;
-  uint32_t run = 0;
-  for (int w = 0; w < words; ++w) {
-    uint32_t bits = row[w].x;
-    row[w].y = run;
-    run += __popc(bits);
-  }
+  table[t] = make_uint2(bits, (uint32_t)below);
 }
 
 // One CTA per output tile.  in_* describe the input tensor, out_* the output tensor (the same
@@ -727,11 +732,11 @@ int build_colmask(const int* zi, const int* zp, const Geom& g, int64_t in_nnz, v
   if (!want_colmask(g, in_nnz) || scratch == nullptr) return SPH_OK;
   const int64_t ncols = (int64_t)g.B * g.H * g.W;
   const int words = div_up(g.D, 32);
-  SPH_CUDA(cudaMemsetAsync(scratch, 0, colmask_bytes(g, in_nnz), st));
+  SPH_CUDA(cudaMemsetAsync(scratch, 0, 256, st));      // the header (flag); the kernel writes every table entry
   cm->unsorted = (const int*)scratch;
   cm->words = words;
   cm->table = (const uint2*)((char*)scratch + 256);
-  build_colmask_kernel<<<(unsigned)div_up64(ncols, 256), 256, 0, st>>>(zi, zp, ncols, words, g.D,
+  build_colmask_kernel<<<(unsigned)div_up64(ncols * words, 256), 256, 0, st>>>(zi, zp, ncols, words, g.D,
                                                                         (uint2*)((char*)scratch + 256), (int*)scratch,
                                                                         row_col);
   SPH_LAUNCH_CHECK();
