@@ -52,6 +52,11 @@ int conv_gather_tc(const void* rows, int dtype, int64_t n_rows, const void* pack
 bool conv_tc_supported(int dtype, int kv, int K, int N);
 int64_t packed_weight_bytes(int dtype, int kv, int K, int N);
 int pack_weight(const void* w, int dtype, int kv, int K, int N, void* packed, cudaStream_t st);
+// conv_tc_rows.cu
+bool conv_tc_rows_supported(int dtype, int kv, int K, int N);
+int conv_gather_tc_rows(const void* rows, int dtype, int64_t n_rows, const void* packed, const int* nbr, int64_t n_out,
+                        int kv, int K, int N, int flip_k, const float* scale, const float* bias, int relu, void* out,
+                        int out_dtype, int* status, cudaStream_t st);
 // conv_wgrad_tc.cu
 bool conv_wgrad_tc_supported(int dtype, int kv, int K, int N);
 int conv_wgrad_tc(const void* rows, const void* dout, int dtype, int64_t n_rows, const int* nbr, int64_t n_out, int kv,
@@ -98,6 +103,12 @@ extern "C" int sph_conv_gather(const void* d_rows, int dtype, int64_t n_rows, co
   SPH_CHECK_ARG(n_rows == 0 || d_rows, "null rows");
   SPH_CHECK_ARG(n_rows < 0x7fffffffLL && n_out < 0x7fffffffLL, "row ids are 32-bit");
   cudaStream_t st = (cudaStream_t)stream;
+  // 64-byte rows: the form with the output row on the TMEM lane (absent neighbours masked, not copied) is the faster
+  // of the two; wider rows are dense deep layers, where the transposed form issues half as many instructions
+  if (d_packed && k_ch * dtype_bytes(dtype) == 64 && conv_tc_rows_supported(dtype, kv, k_ch, n_ch)) {
+    return conv_gather_tc_rows(d_rows, dtype, n_rows, d_packed, d_nbr, n_out, kv, k_ch, n_ch, flip_k, d_scale, d_bias,
+                               relu, d_out, out_dtype, d_status, st);
+  }
   if (d_packed && conv_tc_supported(dtype, kv, k_ch, n_ch)) {
     return conv_gather_tc(d_rows, dtype, n_rows, d_packed, d_nbr, n_out, kv, k_ch, n_ch, flip_k, d_scale, d_bias,
                           relu, d_out, out_dtype, d_status, st);

@@ -188,6 +188,23 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate));
 }
 
+// The same with the disable-output-lane mask: bit b of mask word w switches off accumulator row (TMEM lane) 32w + b,
+// which is then neither overwritten nor accumulated into (M = 128: one word per 32 rows).
+__device__ __forceinline__ void umma_f16_masked(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate, const uint4& mask) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(mask.x), "r"(mask.y), "r"(mask.z), "r"(mask.w));
+}
+__device__ __forceinline__ void umma_i8_masked(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate, const uint4& mask) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(mask.x), "r"(mask.y), "r"(mask.z), "r"(mask.w));
+}
+
 // 16 consecutive 32-bit columns of this thread's TMEM lane (lane = 32 * (warp % 4) + laneid).
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
