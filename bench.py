@@ -577,12 +577,13 @@ def main():
                                "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "bound": "tensor" if t_f >= t_q else "hbm",
                                "frac_bound": round(max(t_f, t_q) / (ms * 1e-3), 4), "kernel": kernel})
             conv_ms += ms
-            g = groups.setdefault(kernel, {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "launches": 0, "layers": [], "rows": 0})
+            g = groups.setdefault(kernel, {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "launches": 0, "layers": [], "traffic": 0.0})
             g["ms"] += ms
             g["flops"] += flops
             g["bytes"] += byts
             g["launches"] += chunks
-            g["rows"] += chunks * meta["n_out"]
+            per_row = TRAFFIC_BYTES_PER_OUT_ROW.get(dtype_name, {}).get(tag) if kind == "conv" else None
+            g["traffic"] = None if (per_row is None or g["traffic"] is None) else g["traffic"] + per_row * chunks * meta["n_out"]
             g["layers"].append(name if kind != "conv" else tag)
             if uses_tc:
                 tc_flops += flops
@@ -625,7 +626,6 @@ def main():
         t_f, t_q = g["flops"] / t_peak, g["bytes"] / h_peak
         bound = "tensor" if t_f >= t_q else "hbm"
         achieved = g["flops"] / t / 1e12 if bound == "tensor" else g["bytes"] / t / 1e9
-        per_row = TRAFFIC_BYTES_PER_OUT_ROW.get((kernel, dtype_name))
         by_kernel.append({
             "kernel": kernel, "layers": g["layers"], "launches_per_step": g["launches"],
             "ms_per_step": round(g["ms"], 4), "share_of_conv_time": round(g["ms"] / conv_ms, 4) if conv_ms else None,
@@ -635,8 +635,8 @@ def main():
             "frac": round(max(t_f, t_q) / t, 4),
             "frac_tensor": round(t_f / t, 4), "frac_hbm": round(t_q / t, 4),
             "flops_per_launch": g["flops"] / g["launches"], "bytes_per_launch": g["bytes"] / g["launches"],
-            "traffic": None if per_row is None else int(per_row[0] * g["rows"] / g["launches"]),
-            "traffic_source": None if per_row is None else per_row[1]})
+            "traffic": None if g["traffic"] is None else int(g["traffic"] / g["launches"]),
+            "traffic_source": None if g["traffic"] is None else TRAFFIC_SOURCE})
     by_kernel.sort(key=lambda r: -r["ms_per_step"])
     dom = by_kernel[0] if by_kernel else {}
     roofline = dict(dom)
@@ -705,11 +705,16 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per output row of one launch, per kernel instantiation,
-# with where the figure comes from: (bytes per output row, provenance).  Traffic grows in proportion to the rows a
-# launch processes (every row is gathered, accumulated and written independently).  Filled from ncu captures of the
-# current kernels on a 4-scan batch (the 8-scan launch is captured only for its duration); None = not captured.
-TRAFFIC_BYTES_PER_OUT_ROW = {}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per OUTPUT ROW of one launch of each convolution layer,
+# from one ncu capture of the kernels of this tree on a 4-scan batch (ncu replays a launch once per pass, so the
+# capture uses a smaller batch than the timed run; every output row is gathered, accumulated and written independently,
+# so a launch's traffic is proportional to its rows).  Part of a launch's output is still in L2 when the kernel ends,
+# so the write half undercounts.  A layer that is not listed has no captured figure (traffic: null).
+TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per output row, 4-scan fp16 capture of these kernels, "
+                  "scaled by the rows of the timed launches")
+TRAFFIC_BYTES_PER_OUT_ROW = {
+    "fp16": {"L0": 116.1, "L1": 140.8, "L2": 146.9, "L3": 210.1, "L4": 210.9, "L5": 292.1, "L6": 282.9, "L7": 285.9},
+}
 
 if __name__ == "__main__":
     main()
