@@ -81,7 +81,7 @@ def test_forward_int8_exact(iC, oC, subm):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("iC,oC", [(16, 16), (64, 64), (16, 5)])
+@pytest.mark.parametrize("iC,oC", [(16, 16), (64, 64), (16, 5), (32, 32), (32, 128)])
 def test_forward_epilogue_and_out_dtype(dtype, iC, oC):
     B, shape = 1, [8, 16, 12]
     rng, feat, w, rules, rule_size, pairs, n_in, n_out = _setup(B, shape, True, 0.3, 8, iC, oC, dtype)
