@@ -227,6 +227,8 @@ def kernel_of(lib, dcode, kind, k_ch, n_ch, esize, dtype_name):
         tc = tc and dtype_name in ("fp16", "bf16")
         return ("conv_wgrad_tc_kernel<%d>" % (k_ch * esize // 16)) if tc else "conv_wgrad_generic_kernel", tc
     if not tc:
+        if lib.sph_conv_uses_pair_kernel(dcode, k_ch, n_ch):
+            return "conv_sparse_rows_kernel<%d,%d>" % (k_ch, n_ch), tc
         return "conv_gather_generic_kernel", tc
     # 64-byte rows run the form with the output row on the TMEM lane (conv_tc_rows.cu), wider rows the transposed one
     name = "conv_gather_rows_kernel" if k_ch * esize == 64 and n_ch % 16 == 0 else "conv_gather_tc_kernel"

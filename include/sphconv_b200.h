@@ -170,8 +170,12 @@ int64_t sph_packed_weight_bytes(int dtype, int32_t kv, int32_t k_ch, int32_t n_c
 int sph_pack_weight(const void* d_weight, int dtype, int32_t kv, int32_t k_ch, int32_t n_ch, void* d_packed,
                     void* stream);
 
-/* 1 when sph_conv_gather runs the tcgen05 kernel for this combination, 0 when it runs the CUDA-core kernel. */
+/* 1 when sph_conv_gather runs the tcgen05 kernel for this combination, 0 when it runs a CUDA-core kernel. */
 int sph_conv_uses_tensor_cores(int dtype, int32_t k_ch, int32_t n_ch);
+/* Which CUDA-core kernel runs when the tensor-core kernels do not take the combination (27 offsets assumed, operands
+ * 16-byte aligned): 1 = the pair-compacting kernel for sparse levels (rows of 4 / 8 / 16 / 32 channels in and out, the
+ * fp32 filter within its shared-memory budget), 0 = the row-walking kernel (any shape).  No reference counterpart. */
+int sph_conv_uses_pair_kernel(int dtype, int32_t k_ch, int32_t n_ch);
 
 /* out[r,:] = epilogue( sum_k rows[ nbr[k][r], : ] @ weight[k] )   for r in [0, n_out)
  * forward: ref rule_conv, src/sphconv/rule_conv.cu:286-336 (rows = feature, nbr = d_nbr, weight [KV,iC,oC]).

@@ -11,7 +11,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(LIBDIR, "libsphconv_b200.so")
-SOURCES = ["rules.cu", "conv_generic.cu", "conv_tc.cu", "conv_tc_rows.cu", "conv_wgrad_tc.cu", "tensor_ops.cu", "voxelize.cu", "capi.cu"]
+SOURCES = ["rules.cu", "conv_generic.cu", "conv_sparse.cu", "conv_tc.cu", "conv_tc_rows.cu", "conv_wgrad_tc.cu", "tensor_ops.cu", "voxelize.cu", "capi.cu"]
 # the explicit -gencode pair is required: the sm_100a shorthand does not enable tcgen05 in ptxas
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math=false"]

@@ -57,6 +57,12 @@ bool conv_tc_rows_supported(int dtype, int kv, int K, int N);
 int conv_gather_tc_rows(const void* rows, int dtype, int64_t n_rows, const void* packed, const int* nbr, int64_t n_out,
                         int kv, int K, int N, int flip_k, const float* scale, const float* bias, int relu, void* out,
                         int out_dtype, int* status, cudaStream_t st);
+// conv_sparse.cu
+bool conv_sparse_supported(int dtype, int kv, int K, int N);
+int conv_gather_sparse(const void* rows, int dtype, int64_t n_rows, const void* weight, const int* nbr, int64_t n_out,
+                       int kv, int K, int N, int flip_k, const float* scale, const float* bias, int relu, void* out,
+                       int out_dtype, int* status, cudaStream_t st);
+
 // conv_wgrad_tc.cu
 bool conv_wgrad_tc_supported(int dtype, int kv, int K, int N);
 int conv_wgrad_tc(const void* rows, const void* dout, int dtype, int64_t n_rows, const int* nbr, int64_t n_out, int kv,
@@ -83,6 +89,10 @@ extern "C" int sph_pack_weight(const void* d_weight, int dtype, int32_t kv, int3
 
 extern "C" int sph_conv_uses_tensor_cores(int dtype, int32_t k_ch, int32_t n_ch) {
   return conv_tc_supported(dtype, 27, k_ch, n_ch) ? 1 : 0;
+}
+
+extern "C" int sph_conv_uses_pair_kernel(int dtype, int32_t k_ch, int32_t n_ch) {
+  return (!conv_tc_supported(dtype, 27, k_ch, n_ch) && conv_sparse_supported(dtype, 27, k_ch, n_ch)) ? 1 : 0;
 }
 
 static bool out_dtype_ok(int dtype, int out_dtype) {
@@ -113,7 +123,14 @@ extern "C" int sph_conv_gather(const void* d_rows, int dtype, int64_t n_rows, co
     return conv_gather_tc(d_rows, dtype, n_rows, d_packed, d_nbr, n_out, kv, k_ch, n_ch, flip_k, d_scale, d_bias,
                           relu, d_out, out_dtype, d_status, st);
   }
-  SPH_CHECK_ARG(d_weight, "the CUDA-core kernel needs the unpacked weight");
+  SPH_CHECK_ARG(d_weight, "the CUDA-core kernels need the unpacked weight");
+  // narrow rows the tensor-core kernels do not take (the first layer of an encoder: 4 or 8 channels in, a sparse level)
+  // and small fp32 layers: the pair-compacting kernel (faster than the row-walking one from 1 to 22 neighbours per row)
+  if (conv_sparse_supported(dtype, kv, k_ch, n_ch) && out_dtype != SPH_I8 &&
+      ((((uintptr_t)d_rows | (uintptr_t)d_weight | (uintptr_t)d_out) & 15u) == 0)) {
+    return conv_gather_sparse(d_rows, dtype, n_rows, d_weight, d_nbr, n_out, kv, k_ch, n_ch, flip_k, d_scale, d_bias,
+                              relu, d_out, out_dtype, d_status, st);
+  }
   return conv_gather_generic(d_rows, dtype, n_rows, d_weight, d_nbr, n_out, kv, k_ch, n_ch, flip_k, d_scale, d_bias,
                              relu, d_out, out_dtype, d_status, st);
 }

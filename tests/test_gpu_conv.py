@@ -149,6 +149,11 @@ def test_tensor_core_path_is_selected():
     assert lib.sph_conv_uses_tensor_cores(C.SPH_I8, 32, 64) == 1
     assert lib.sph_conv_uses_tensor_cores(C.SPH_F32, 64, 64) == 0
     assert lib.sph_conv_uses_tensor_cores(C.SPH_F16, 4, 16) == 0
+    # narrow rows of the first layer and small fp32 layers: the pair-compacting CUDA-core kernel
+    assert lib.sph_conv_uses_pair_kernel(C.SPH_F16, 4, 16) == 1
+    assert lib.sph_conv_uses_pair_kernel(C.SPH_F32, 16, 16) == 1
+    assert lib.sph_conv_uses_pair_kernel(C.SPH_F16, 64, 64) == 0
+    assert lib.sph_conv_uses_pair_kernel(C.SPH_F16, 5, 16) == 0
 
 
 @pytest.mark.parametrize("dtype,iC,oC", [(torch.float16, 64, 64), (torch.bfloat16, 32, 64), (torch.int8, 64, 64),

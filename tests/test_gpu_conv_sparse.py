@@ -1,0 +1,76 @@
+"""The pair-compacting CUDA-core kernel (narrow rows of a sparse first level, small fp32 layers) against the CPU oracle,
+through the same entry point as every other convolution: shapes the tensor-core kernels do not take route to it.
+
+Cases: 4/8/16/32 channels in and out, fp16 / bf16 / fp32, submanifold and strided tables, nearly empty and completely
+full grids (a full grid lists 27 items per row: every batch of 32 items is followed by a remainder, and consecutive
+offsets name the same output row inside one pass), a kernel volume above 32 (the table is read in several groups),
+output row counts that are not a multiple of 32, the fused epilogue with every output dtype, and dgrad (the flipped
+table of a submanifold layer, the transposed table of a strided one)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import conv_np
+from sphconv_b200 import check_status
+from sphconv_b200 import sphconv_cuda as ops
+
+from gpu_util import DEV
+from test_gpu_conv import TOL, _close, _setup
+
+pytestmark = pytest.mark.gpu
+
+NARROW = [(4, 16), (16, 4), (8, 16), (4, 32), (32, 4), (8, 8), (4, 4)]
+
+
+@pytest.mark.parametrize("iC,oC", NARROW)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("subm,dens", [(True, 0.02), (True, 0.3), (True, 1.0), (False, 0.05), (False, 1.0)])
+def test_forward_narrow_rows(iC, oC, dtype, subm, dens):
+    B, shape = 2, [9, 21, 13]
+    rng, feat, w, rules, rule_size, pairs, n_in, n_out = _setup(B, shape, subm, dens, 31, iC, oC, dtype)
+    out = ops.rule_conv(feat, w, rules, rule_size, n_out)
+    assert out.dtype == dtype and tuple(out.shape) == (n_out, oC)
+    ref = conv_np.conv_forward(feat.double().cpu().numpy(), w.double().cpu().numpy(), pairs, n_out)
+    _close(out, ref, TOL[dtype])
+    assert check_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("subm,ks", [(True, (5, 3, 3)), (False, (3, 5, 3)), (True, (5, 5, 5))])
+def test_forward_kernel_volume_above_32(dtype, subm, ks):
+    B, shape = 1, [8, 14, 12]
+    rng, feat, w, rules, rule_size, pairs, n_in, n_out = _setup(B, shape, subm, 0.4, 32, 4, 16, dtype, ks=ks)
+    out = ops.rule_conv(feat, w, rules, rule_size, n_out)
+    ref = conv_np.conv_forward(feat.double().cpu().numpy(), w.double().cpu().numpy(), pairs, n_out)
+    _close(out, ref, TOL[dtype])
+    assert check_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("iC,oC", [(4, 16), (16, 4), (8, 32)])
+def test_epilogue_and_out_dtype(dtype, out_dtype, iC, oC):
+    B, shape = 1, [8, 16, 12]
+    rng, feat, w, rules, rule_size, pairs, n_in, n_out = _setup(B, shape, True, 0.3, 33, iC, oC, dtype)
+    bias = torch.as_tensor(rng.standard_normal(oC), dtype=torch.float32, device=DEV)
+    scale = torch.as_tensor(rng.uniform(0.5, 2, size=oC), dtype=torch.float32, device=DEV)
+    out = ops.rule_conv(feat, w, rules, rule_size, n_out, scale=scale, bias=bias, relu=True, out_dtype=out_dtype)
+    ref = conv_np.conv_forward(feat.double().cpu().numpy(), w.double().cpu().numpy(), pairs, n_out)
+    ref = np.maximum(ref * scale.double().cpu().numpy() + bias.double().cpu().numpy(), 0)
+    assert out.dtype == out_dtype
+    _close(out, ref, max(TOL[dtype], TOL[out_dtype]))
+    assert check_status() == 0
+
+
+@pytest.mark.parametrize("iC,oC", [(4, 16), (16, 8)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("subm", [True, False])
+def test_dgrad_narrow_rows(iC, oC, dtype, subm):
+    B, shape = 2, [9, 21, 13]
+    rng, feat, w, rules, rule_size, pairs, n_in, n_out = _setup(B, shape, subm, 0.3, 34, iC, oC, dtype)
+    dout = torch.as_tensor(rng.standard_normal((n_out, oC)), dtype=torch.float32, device=DEV).to(dtype)
+    dfeat = ops.rule_conv_d_feature(dout, w.permute(0, 2, 1).contiguous(), rules, rule_size, [1, 1], n_in)
+    assert tuple(dfeat.shape) == (n_in, iC)
+    ref = conv_np.conv_dgrad(dout.double().cpu().numpy(), w.double().cpu().numpy(), pairs, n_in)
+    _close(dfeat, ref, TOL[dtype])
+    assert check_status() == 0
