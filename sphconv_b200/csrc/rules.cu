@@ -328,8 +328,10 @@ nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, G
 
 constexpr int kListWarps = 8;
 constexpr int kListRanges = 128;   // (batch, tile row) ranges staged per pass
-constexpr int kListChunks = 8;     // 32-row chunks whose table reads are in flight together
 
+// kListChunks: 32-row chunks whose table reads are in flight together (8 for tiles of hundreds of rows; 1 or 2 for
+// tiles of a few dozen, where the chunks beyond the tile's rows would only cost instructions)
+template <int kListChunks>
 __global__ void __launch_bounds__(kListWarps * 32)
 rule_lists_kernel(const int* __restrict__ out_zp, Geom g, int64_t out_nnz, int tile_n_max, int kg, int n_kg,
                   const int* __restrict__ nbr, int* __restrict__ rules, int* __restrict__ rule_size,
@@ -758,8 +760,17 @@ int launch_rule_lists(const int* out_zp, const Geom& g, int64_t out_nnz, int tnm
   if (kg > g.KV) kg = g.KV;
   const int n_kg = div_up(g.KV, kg);
   const int64_t items = (int64_t)g.nTile * n_kg;
-  rule_lists_kernel<<<(unsigned)div_up64(items, kListWarps), kListWarps * 32, 0, st>>>(
-      out_zp, g, out_nnz, tnm, kg, n_kg, nbr, rules, rule_size, unsorted, status);
+  const unsigned grid = (unsigned)div_up64(items, kListWarps);
+  // chunks per step: the smallest that holds 1.25 x the average tile (larger tiles take more steps)
+  const int64_t want = (out_nnz / (g.nTile > 0 ? g.nTile : 1)) * 5 / 4;
+#define SPH_LISTS(CH)                                                                                             \
+  rule_lists_kernel<CH><<<grid, kListWarps * 32, 0, st>>>(out_zp, g, out_nnz, tnm, kg, n_kg, nbr, rules, rule_size, \
+                                                          unsorted, status)
+  if (want <= 32) SPH_LISTS(1);
+  else if (want <= 64) SPH_LISTS(2);
+  else if (want <= 128) SPH_LISTS(4);
+  else SPH_LISTS(8);
+#undef SPH_LISTS
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
