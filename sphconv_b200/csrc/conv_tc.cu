@@ -27,34 +27,18 @@
 // rows: core (row group g, chunk c) at c*4112 + g*128; weights: core (channel group gn, chunk c) at
 // c*(N/8)*128 + gn*128 (images hold the N real channels only: the rows up to M = 64/128 that the instruction also
 // reads are whatever follows in shared memory and only feed accumulator rows nobody reads).
-#include "common.cuh"
-#include "tc_common.cuh"
+#include "conv_tc_gather.cuh"
 
 namespace sph {
 
 namespace {
 
 using namespace tc;
+using namespace tcgather;
 
-constexpr int kTcMaxKV = 32;        // kernel volume the tensor-core kernel handles (3x3x3 = 27)
-constexpr int kTileRows = 256;      // output rows per tile = UMMA N
-#ifndef SPH_TC_PRODUCER_WARPS
-#define SPH_TC_PRODUCER_WARPS 8
-#endif
-constexpr int kProducerWarps = SPH_TC_PRODUCER_WARPS;    // gather warps
-#ifndef SPH_GK4
-#define SPH_GK4 2                   // kernel offsets per pipeline stage for 64-byte rows
-#endif
 constexpr int kMmaWarp = kProducerWarps;
 constexpr int kTcThreads = (kProducerWarps + 1 + 4) * 32;
 constexpr int kSubRows = 64;        // accumulator columns (output rows) an epilogue thread reads back at a time
-constexpr int kMaxStages = 8;
-constexpr int kRingStages = 4;     // pipeline slots used (see plan_smem)
-constexpr int kSmemTotal = 227 * 1024 - 2048;   // dynamic shared memory available next to the static part
-// Byte distance between K-adjacent core matrices of the gathered-row tile.  The extra 16 bytes skew the
-// chunks of one row across the shared-memory banks, so the 32 lanes of a gather instruction (a few rows x
-// all their chunks) write without bank conflicts.
-constexpr uint32_t kRowsLbo = kTileRows * 16 + 16;
 
 struct TcParams {
   const void* rows;
@@ -134,11 +118,8 @@ __device__ __forceinline__ void store_rows64_any(uint8_t* dst, int row_pitch, in
 // streams, not the tensor pipe or the memory system, set the pace once the data path is asynchronous.
 template <int KC, bool I8>
 __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
-  constexpr int GK = KC == 2 ? 4 : KC == 4 ? SPH_GK4 : 1;   // kernel offsets per pipeline stage
-  constexpr int LPR = KC < 8 ? KC : 8;           // lanes per row = rows per lane
-  constexpr int PASSES = KC / LPR;               // 2 only for 256-byte rows
-  constexpr int NMMA = KC / 2;                   // 32 bytes of K per instruction
-  constexpr uint32_t X_BYTES = (uint32_t)KC * kRowsLbo;
+  constexpr int GK = RowShape<KC>::GK, NMMA = RowShape<KC>::NMMA;
+  constexpr uint32_t X_BYTES = RowShape<KC>::X_BYTES;
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ __align__(8) uint64_t s_full[kMaxStages];
   __shared__ __align__(8) uint64_t s_empty[kMaxStages];
@@ -185,179 +166,25 @@ __global__ void __maxnreg__(112) conv_gather_tc_kernel(TcParams p) {
   const int my_tiles = (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
   if (warp < kProducerWarps) {
-    // ======================= gather producers =======================
-    // Stage ownership: the gather warps form two teams; team q fills pipeline stages q, q + 2, ... (all 256 rows
-    // of the stage, 64 per warp).  The arrive that ties a stage's barrier to the completion of a thread's copies
-    // (cp.async.mbarrier.arrive.noinc) holds back the later memory instructions of that warp until the copies
-    // have landed; with every warp working on every stage, the copies of stage f+1 could not be issued while
-    // those of stage f were landing.  With ownership one team issues while the other team's copies land.
-    // Everything below is compile-time (team count, rows per warp and lane), so a stage is straight-line code.
-    constexpr int G = 2;                           // two teams of warps take alternate stages
-    constexpr int wpg = kProducerWarps / G;        // warps per team
-    const int grp = warp / wpg, wig = warp % wpg;
-    constexpr int RPW = kTileRows / wpg;           // rows of each stage this warp gathers
-    constexpr int RPL = RPW * LPR / 32;            // rows per lane and offset (LPR lanes share a row)
-    // One gather instruction covers NG consecutive rows: lane group q = lane / LPR takes rows q, q + NG, ...  A row
-    // is 16 bytes further in each chunk plane and a chunk plane is kRowsLbo = 16 mod 128 bytes further, so lane
-    // (q, c) writes bank group (q + c) mod 8 and the 32 lanes spread evenly over all banks (with groups RPL rows
-    // apart, i.e. a multiple of 128 bytes, the 64- and 32-byte rows used half and a quarter of the banks).
-    // Consecutive output rows also tend to have consecutive input rows as neighbours: fewer cache lines per
-    // instruction.
-    constexpr int NG = 32 / LPR;
-    if (p.w_resident && tid == 0) {
-      mbar_arrive_expect_tx(smem_u32(&s_w_full), (uint32_t)(p.kv * p.w_bytes));
-      for (int k = 0; k < p.kv; ++k)   // one bulk copy per offset keeps each transfer small
-        bulk_g2s(smem_u32(w_smem + (size_t)k * p.w_bytes), (const uint8_t*)p.packed + (size_t)k * p.w_bytes,
-                 (uint32_t)p.w_bytes, smem_u32(&s_w_full));
-    }
-    const uint8_t* rows = (const uint8_t*)p.rows;
-    // Neighbour-table entries this warp needs for ONE TILE: the offsets of the stages it owns in that tile
-    // times its RPW rows, [owned stage][GK][RPW], private to the warp (at most 1024 entries: the launcher
-    // checks).  They are loaded a whole tile ahead into registers (coalesced; the table streams from HBM, and
-    // a load issued only a stage ahead sits behind the stage's copies) and parked at the tile boundary.
-    constexpr int kMaxEnt = 32;                    // registers per lane
-    constexpr int eps = GK * RPW;                  // entries per owned stage
-    int* tbl = s_tbl + warp * (kMaxEnt * 32);
-    int ent[kMaxEnt];
-    const unsigned n_rows_u = (unsigned)p.n_rows;
-    uint32_t bad = 0u;
-    const int total = my_tiles * groups;           // flat stage count of this CTA
-    auto first_owned = [&](int ti) {               // first flat stage >= ti * groups that this group owns
-      const int base = ti * groups;
-      int d = (grp - base) % G;
-      if (d < 0) d += G;
-      return base + d;
-    };
-    // Entry e of a lane is compile-time (owned stage os, offset g of the stage, 32-row chunk h): only the row inside
-    // the chunk depends on the lane, so a tile's loads cost a few instructions each (this runs on the gather warps'
-    // own instruction streams, between two stages).
-    constexpr int CH = RPW / 32;                   // 32-slot chunks of the warp's rows
-    int64_t rofs[CH];                              // slot -> row: lane group q keeps its RPL slots together (vector
-#pragma unroll                                     // reads of the parked table), its j-th slot is row q + j * NG
-    for (int h = 0; h < CH; ++h) {
-      const int slot = h * 32 + lane;
-      rofs[h] = wig * RPW + (slot % RPL) * NG + slot / RPL;
-    }
-    auto load_tile = [&](int ti) {
-      const int sj0 = first_owned(ti) - ti * groups;           // first owned stage inside the tile
-      const int64_t r0 = ((int64_t)blockIdx.x + (int64_t)ti * gridDim.x) * kTileRows;
-      bool row_ok[CH];
-#pragma unroll
-      for (int h = 0; h < CH; ++h) row_ok[h] = ti < my_tiles && r0 + rofs[h] < p.n_out;
-#pragma unroll
-      for (int e = 0; e < kMaxEnt; ++e) {
-        constexpr int per_stage = GK * CH;
-        const int os = e / per_stage, g = (e / CH) % GK, h = e % CH;   // compile-time after unrolling
-        const int k = (sj0 + os * G) * GK + g;
-        const int* plane = p.nbr + (int64_t)(p.flip_k ? p.kv - 1 - k : k) * p.n_out + r0;
-        // plain loads with no dependent work here: all 32 stay in flight; they are checked when parked
-        ent[e] = (row_ok[h] && k < p.kv) ? __ldg(plane + rofs[h]) : -1;
-      }
-    };
-    auto park_tile = [&]() {
-      __syncwarp();   // every lane has finished reading the previous tile's entries
-#pragma unroll
-      for (int e = 0; e < kMaxEnt; ++e) {
-        int v = ent[e];
-        if ((unsigned)v >= n_rows_u) {             // -1 (absent) or an id out of range
-          bad |= (uint32_t)(v + 1);                // non-zero only for an id that is neither -1 nor valid
-          v = -1;
-        }
-        tbl[e * 32 + lane] = v;
-      }
-      __syncwarp();
-    };
-    const int l_chunk = lane % LPR;
-    const int l_grp = lane / LPR;                  // this lane's rows inside the warp's RPW: l_grp + j * NG
-    const int l_slot0 = l_grp * RPL;               // its first slot in the parked table
-    const uint32_t lane_dst = (uint32_t)l_chunk * kRowsLbo + (uint32_t)(wig * RPW + l_grp) * 16u;
-    const uint8_t* rows_c = rows + l_chunk * 16;
-    const uint32_t row_bytes = (uint32_t)KC * 16u;
-    const uint32_t stage0_u = smem_u32(stage0);
-    const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
-    int s = grp % S;                                // slot of flat stage f is f % S
-    uint32_t par = ((uint32_t)(grp / S) & 1u) ^ 1u; // parity to wait for on the slot's empty barrier
-    int ti = 0;                                     // tile of the current stage
-    int tile_end = groups;                          // first flat stage of the next tile
-    int own_j = 0;                                  // index of the current stage among this tile's owned stages
-    const int batch = S >= 5 ? 2 : 1;               // owned stages acquired per poll (costs two slots of run-ahead)
-    int credits = 0;
-    load_tile(0);
-    park_tile();
-    load_tile(1);
-    for (int f = grp; f < total; f += G) {
-      while (f >= tile_end) {                       // entered the next tile: its entries are in registers
-        park_tile();
-        ++ti;
-        tile_end += groups;
-        own_j = 0;
-        load_tile(ti + 1);
-      }
-      // One lane polls (hundreds of threads polling one mbarrier serialise on it), and only every `batch` owned
-      // stages: an mbarrier operation costs ~200 cycles of the polling thread, and the MMA thread releases the
-      // slots in order, so "the slot of my stage after next is free" implies the slot of this one is too.
-      if (credits == 0) {
-        bool ok_w = true;
-        if (lane == 0) {
-          int sa = s + (batch - 1) * G;
-          uint32_t pa = par;
-          if (sa >= S) { sa -= S; pa ^= 1u; }
-          ok_w = mbar_wait(empty0 + 8u * sa, pa, abort_flag);
-        }
-        if (__any_sync(0xffffffffu, !ok_w)) break;   // also orders the other lanes behind the poll
-        credits = batch;
-      }
-      --credits;
-      const uint32_t stage = stage0_u + (uint32_t)(s * stage_bytes);
-      const int k0 = (f - (tile_end - groups)) * GK;
-      if (!p.w_resident && wig == 0 && lane == 0) {
-        const uint32_t bytes = (uint32_t)(min(GK, p.kv - k0) * p.w_bytes);
-        mbar_arrive_expect_tx(full0 + 8u * s, bytes);
-        bulk_g2s(stage + GK * X_BYTES, (const uint8_t*)p.packed + (size_t)k0 * p.w_bytes, bytes, full0 + 8u * s);
-      }
-#pragma unroll
-      for (int g = 0; g < GK; ++g) {
-        if (GK == 1 || k0 + g < p.kv) {
-          const int* trow = tbl + own_j * eps + g * RPW + l_slot0;
-          const uint32_t dst0 = stage + (uint32_t)g * X_BYTES + lane_dst;
-#pragma unroll
-          for (int j0 = 0; j0 < RPL; j0 += LPR) {
-            int r[LPR];
-            if (LPR == 8) {
-              const int4 a = *(const int4*)(trow + j0), b = *(const int4*)(trow + j0 + 4);
-              r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
-              r[4 % LPR] = b.x; r[5 % LPR] = b.y; r[6 % LPR] = b.z; r[7 % LPR] = b.w;
-            } else if (LPR == 4) {
-              const int4 a = *(const int4*)(trow + j0);
-              r[0] = a.x; r[1] = a.y; r[2 % LPR] = a.z; r[3 % LPR] = a.w;
-            } else {
-              const int2 a = *(const int2*)(trow + j0);
-              r[0] = a.x; r[1] = a.y;
-            }
-#pragma unroll
-            for (int j = 0; j < LPR; ++j) {
-              const bool present = r[j] >= 0;
-              const uint8_t* src = rows_c + (size_t)(present ? (uint32_t)r[j] : 0u) * row_bytes;
-              const uint32_t sz = present ? 16u : 0u;
-              // .ca: the three depth offsets of one (kh,kw) read nearly the same input rows a stage or two
-              // apart, and the slice of L1 that the shared-memory carve-out leaves catches most of the repeats
-              cp_async_16_ca(dst0 + (uint32_t)((j0 + j) * NG) * 16u, src, sz);
-              if (PASSES == 2) cp_async_16_ca(dst0 + (uint32_t)((j0 + j) * NG) * 16u + 8u * kRowsLbo, src + 128, sz);
-            }
-          }
-        }
-      }
+    // ======================= gather warps (conv_tc_gather.cuh), zero-filling form =======================
 #ifdef SPH_TEST_HOOKS
-      // Test build only: the bounded waits and the wind-down are exercised by a stage that never becomes full.
-      if (!(p.test_withhold && f == 1 && wig == 0 && lane == 0))
+    const int withhold = p.test_withhold;
+#else
+    const int withhold = 0;
 #endif
-      cp_async_arrive_noinc(full0 + 8u * s);
-      ++own_j;
-      s += G;
-      if (s >= S) { s -= S; par ^= 1u; }
-    }
-    cp_async_wait_all();
-    if (bad && p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
+    GatherCtx c;
+    c.rows = p.rows; c.packed = p.packed; c.nbr = p.nbr;
+    c.n_rows = p.n_rows; c.n_out = p.n_out;
+    c.kv = p.kv; c.flip_k = p.flip_k;
+    c.w_resident = p.w_resident; c.w_bytes = p.w_bytes;
+    c.stages = S; c.stage_bytes = stage_bytes; c.my_tiles = my_tiles;
+    c.status = p.status;
+    c.tbl = s_tbl; c.msk = nullptr; c.w_smem = w_smem;
+    c.stage0 = smem_u32(stage0);
+    c.full0 = smem_u32(&s_full[0]); c.empty0 = smem_u32(&s_empty[0]); c.w_full = smem_u32(&s_w_full);
+    c.abort_flag = abort_flag;
+    c.test_withhold = withhold;
+    run_gather_warps<KC, false>(c);
   } else if (warp == kMmaWarp) {
     // ======================= MMA issuer =======================
     if (lane == 0) {
@@ -493,7 +320,7 @@ bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   p->tbl_off = off; off += kProducerWarps * 32 * 32 * (int)sizeof(int);   // 32 entries per lane and tile
   off = (off + 1023) & ~1023;
   p->w_off = off;
-  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? SPH_GK4 : 1;   // kernel offsets per stage (must match the kernel's GK)
+  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? kGK4 : 1;   // kernel offsets per stage (RowShape<KC>::GK)
   const int w_all = kv * p->w_bytes;
   const int avail = kSmemTotal - 1024 - off;            // 1 KB slack: the M = 64/128 instruction reads past a short image
   // resident weights or one image per stage: whichever keeps more gathered offsets in flight (memory latency is
