@@ -329,6 +329,147 @@ nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, G
 constexpr int kListWarps = 8;
 constexpr int kListRanges = 128;   // (batch, tile row) ranges staged per pass
 
+// Stages runs [rg, rg + nr) of a tile - each (batch, tile row) is one contiguous run of output rows - for one warp:
+// rs[i] = first row of run i, off[i] = list position of its first row (exclusive prefix of the run lengths, off[nr] =
+// the number of rows).  Returns that number.  Ends with a __syncwarp().
+__device__ __forceinline__ int stage_tile_runs(const int* __restrict__ out_zp, const Geom& g, int ox0, int oy0, int tHe,
+                                               int tWe, int rg, int nr, int* rs, int* off, int lane) {
+  int carry = 0;
+  for (int base = 0; base < nr; base += 32) {
+    const int i = base + lane;
+    int s = 0, len = 0;
+    if (i < nr) {
+      const int rr = rg + i;
+      const int b = rr / tHe, dx = rr % tHe;
+      const int64_t c0 = ((int64_t)b * g.oH + (ox0 + dx)) * g.oW + oy0;
+      s = col_start(out_zp, c0);
+      len = __ldg(out_zp + c0 + tWe - 1) - s;
+    }
+    int incl = len;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (i < nr) {
+      rs[i] = s;
+      off[i + 1] = carry + incl;
+    }
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) off[0] = 0;
+  __syncwarp();
+  return carry;
+}
+
+
+// The same lists for a kernel volume that is a multiple of NK, with NK offsets per warp held in registers: a warp takes
+// CH x 32 list positions at a time, reads their NK table entries (CH x NK independent coalesced loads, the next
+// positions' requested before these are compacted) and appends offset by offset with a ballot and a prefix popcount.
+// The running count of every offset is a register of its own (the offset loop is unrolled), and the position -> row
+// mapping of the tile is walked once for all NK offsets.  About a fifth of the instructions of rule_lists_kernel per
+// table entry.
+constexpr int kFixWarps = 4;
+
+template <int NK, int CH>
+__global__ void __launch_bounds__(kFixWarps * 32)
+rule_lists_fixed_kernel(const int* __restrict__ out_zp, Geom g, int64_t out_nnz, int tile_n_max, int n_kg,
+                        const int* __restrict__ nbr, int* __restrict__ rules, int* __restrict__ rule_size,
+                        const int* __restrict__ unsorted, int* __restrict__ status) {
+  __shared__ int s_rs[kFixWarps][kListRanges];
+  __shared__ int s_off[kFixWarps][kListRanges + 1];
+  if (unsorted && *unsorted) return;
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int64_t item = (int64_t)blockIdx.x * kFixWarps + wib;
+  if (item >= (int64_t)g.nTile * n_kg) return;
+  const int t = (int)(item / n_kg);
+  const int k_lo = (int)(item % n_kg) * NK;
+  const int th = t / g.tgW, tw = t % g.tgW;
+  const int ox0 = th * g.tH, oy0 = tw * g.tW;
+  const int tHe = min(g.tH, g.oH - ox0);
+  const int tWe = min(g.tW, g.oW - oy0);
+  const int R = g.B * tHe;
+  const unsigned lt = (1u << lane) - 1u;
+  int* rs = s_rs[wib];
+  int* off = s_off[wib];
+  const int* plane0 = nbr + (int64_t)k_lo * out_nnz;
+  int* lst0 = rules ? rules + ((int64_t)t * g.KV + k_lo) * 2 * tile_n_max : nullptr;
+  const int64_t lst_stride = 2 * (int64_t)tile_n_max;
+  int base[NK];
+#pragma unroll
+  for (int j = 0; j < NK; ++j) base[j] = 0;
+  bool overflow = false;
+  for (int rg = 0; rg < R; rg += kListRanges) {
+    const int nr = min(kListRanges, R - rg);
+    const int T = stage_tile_runs(out_zp, g, ox0, oy0, tHe, tWe, rg, nr, rs, off, lane);
+    // positions only grow, so each lane walks the runs forward, keeping the bounds of its current run in registers
+    int cur = 0, cur_lo = 0, cur_hi = off[1], cur_rs = rs[0];
+    auto fetch = [&](int p0, int (&row)[CH], int (&v)[CH][NK]) {
+#pragma unroll
+      for (int u = 0; u < CH; ++u) {
+        const int p = p0 + u * 32 + lane;
+        row[u] = -1;
+        if (p < T) {
+          while (p >= cur_hi) {
+            ++cur;
+            cur_lo = cur_hi;
+            cur_hi = off[cur + 1];
+            cur_rs = rs[cur];
+          }
+          row[u] = cur_rs + (p - cur_lo);
+        }
+        const int* src = plane0 + (row[u] >= 0 ? row[u] : 0);
+#pragma unroll
+        for (int j = 0; j < NK; ++j) v[u][j] = row[u] >= 0 ? __ldg(src + (int64_t)j * out_nnz) : -1;
+      }
+    };
+    int row[CH], v[CH][NK];
+    if (T > 0) fetch(0, row, v);
+    for (int p0 = 0; p0 < T; p0 += 32 * CH) {
+      int nrow[CH], nv[CH][NK];
+      const bool more = p0 + 32 * CH < T;
+      if (more) fetch(p0 + 32 * CH, nrow, nv);
+#pragma unroll
+      for (int j = 0; j < NK; ++j) {
+        int* lst = lst0 + j * lst_stride;
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
+          const unsigned m = __ballot_sync(0xffffffffu, v[u][j] >= 0);
+          if (m == 0u) continue;
+          if (v[u][j] >= 0 && lst0) {
+            const int slot = base[j] + __popc(m & lt);
+            if (slot < tile_n_max) {
+              lst[slot] = v[u][j];
+              lst[tile_n_max + slot] = row[u];
+            } else {
+              overflow = true;
+            }
+          }
+          base[j] += __popc(m);
+        }
+      }
+      if (more) {
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
+          row[u] = nrow[u];
+#pragma unroll
+          for (int j = 0; j < NK; ++j) v[u][j] = nv[u][j];
+        }
+      }
+    }
+    __syncwarp();   // the next group overwrites the staged runs
+  }
+  if (rule_size) {
+    int mine = 0;
+#pragma unroll
+    for (int j = 0; j < NK; ++j)
+      if (lane == j) mine = base[j];
+    if (lane < NK) rule_size[(int64_t)t * g.KV + k_lo + lane] = mine;
+  }
+  if (overflow && status) atomicOr(status, SPH_STATUS_RULE_OVERFLOW);
+}
+
 // kListChunks: 32-row chunks whose table reads are in flight together (8 for tiles of hundreds of rows; 1 or 2 for
 // tiles of a few dozen, where the chunks beyond the tile's rows would only cost instructions)
 template <int kListChunks>
@@ -359,32 +500,7 @@ rule_lists_kernel(const int* __restrict__ out_zp, Geom g, int64_t out_nnz, int t
   for (int rg = 0; rg < R; rg += kListRanges) {
     const int nr = min(kListRanges, R - rg);
     // ---- the runs of this group and the exclusive prefix of their lengths (list position -> row)
-    int carry = 0;
-    for (int base = 0; base < nr; base += 32) {
-      const int i = base + lane;
-      int s = 0, len = 0;
-      if (i < nr) {
-        const int rr = rg + i;
-        const int b = rr / tHe, dx = rr % tHe;
-        const int64_t c0 = ((int64_t)b * g.oH + (ox0 + dx)) * g.oW + oy0;
-        s = col_start(out_zp, c0);
-        len = __ldg(out_zp + c0 + tWe - 1) - s;
-      }
-      int incl = len;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += n;
-      }
-      if (i < nr) {
-        rs[i] = s;
-        off[i + 1] = carry + incl;
-      }
-      carry += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    if (lane == 0) off[0] = 0;
-    __syncwarp();
-    const int T = carry;
+    const int T = stage_tile_runs(out_zp, g, ox0, oy0, tHe, tWe, rg, nr, rs, off, lane);
     // list position -> row: positions only grow, so each lane walks the runs forward, keeping the bounds of
     // its current run in registers
     int cur = 0, cur_lo = 0, cur_hi = off[1], cur_rs = rs[0];
@@ -753,6 +869,21 @@ int* parked_columns(const Geom& g, int* nbr, int64_t out_nnz) {
 // Pair lists of every (tile, offset) from a finished neighbour table.
 int launch_rule_lists(const int* out_zp, const Geom& g, int64_t out_nnz, int tnm, const int* nbr, int* rules,
                       int* rule_size, const int* unsorted, int* status, cudaStream_t st) {
+  if (g.KV == 27) {
+    // the usual 3 x 3 x 3 filter: the kernel with the offsets' running counts in registers
+    // nine offsets per warp where that gives the machine enough warps, else three (small tile grids have long tiles:
+    // more warps per tile also evens out their lengths).  Measured beside the convolution kernels: one chunk of 32
+    // positions per step beats 2, 4 or 8 (more registers per thread = fewer list warps resident beside the persistent
+    // convolution CTA), and 27 offsets per warp leaves too few warps.
+#define SPH_LISTS_FIXED(NK)                                                                                           \
+  rule_lists_fixed_kernel<NK, 1><<<(unsigned)div_up64((int64_t)g.nTile * (27 / NK), kFixWarps), kFixWarps * 32, 0,     \
+                                   st>>>(out_zp, g, out_nnz, tnm, 27 / NK, nbr, rules, rule_size, unsorted, status)
+    if ((int64_t)g.nTile * 3 >= 6000) SPH_LISTS_FIXED(9);
+    else SPH_LISTS_FIXED(3);
+#undef SPH_LISTS_FIXED
+    SPH_LAUNCH_CHECK();
+    return SPH_OK;
+  }
   // enough warps to fill the machine, at most 32 offsets per warp (one running count per lane)
   const int64_t lists = (int64_t)g.nTile * g.KV;
   int kg = (int)(lists / 20000);
