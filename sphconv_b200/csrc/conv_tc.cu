@@ -320,7 +320,7 @@ bool plan_smem(TcParams* p, int kv, int* smem_bytes) {
   p->tbl_off = off; off += kProducerWarps * 32 * 32 * (int)sizeof(int);   // 32 entries per lane and tile
   off = (off + 1023) & ~1023;
   p->w_off = off;
-  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? kGK4 : 1;   // kernel offsets per stage (RowShape<KC>::GK)
+  const int gk = offsets_per_stage(p->kc);
   const int w_all = kv * p->w_bytes;
   const int avail = kSmemTotal - 1024 - off;            // 1 KB slack: the M = 64/128 instruction reads past a short image
   // resident weights or one image per stage: whichever keeps more gathered offsets in flight (memory latency is

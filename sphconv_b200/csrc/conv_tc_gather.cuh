@@ -15,7 +15,12 @@ using namespace tc;
 constexpr int kTcMaxKV = 32;        // kernel volume the tensor-core kernels handle (3x3x3 = 27)
 constexpr int kTileRows = 256;      // output rows per tile
 constexpr int kProducerWarps = 8;   // gather warps
-constexpr int kGK4 = 2;             // kernel offsets per pipeline stage for 64-byte rows
+// Kernel offsets per pipeline stage by row width (16-byte chunks per row).  A stage costs ~600 cycles of barrier
+// hand-over whatever it holds, so narrow rows take as many offsets per stage as the table registers (32 entries per lane
+// and tile) and three ring slots allow: 7 for 32-byte rows (4 stages per 27-offset tile; measured 0.087 ms against
+// 0.103 ms with 4 on a 16->16 layer), 3 for 64-byte rows (9 stages; 0.343 against 0.366 ms with 2 on a 32->32 layer), 1
+// for wider rows (two offsets of 128-byte rows leave only two slots: no faster).
+__host__ __device__ constexpr int offsets_per_stage(int kc) { return kc == 2 ? 7 : kc == 4 ? 3 : 1; }
 constexpr int kMaxStages = 8;
 constexpr int kRingStages = 4;      // pipeline slots used (see plan_smem of either kernel)
 constexpr int kMaskTiles = 8;       // ring of tiles whose row masks are kept (masked form)
@@ -26,7 +31,7 @@ constexpr uint32_t kRowsLbo = kTileRows * 16 + 16;
 
 // KC = 16-byte chunks per gathered row (2, 4, 8, 16).
 template <int KC> struct RowShape {
-  static constexpr int GK = KC == 2 ? 4 : KC == 4 ? kGK4 : 1;   // kernel offsets per pipeline stage
+  static constexpr int GK = offsets_per_stage(KC);               // kernel offsets per pipeline stage
   static constexpr int LPR = KC < 8 ? KC : 8;                    // lanes per row = rows per lane
   static constexpr int PASSES = KC / LPR;                        // 2 only for 256-byte rows
   static constexpr int NMMA = KC / 2;                            // 32 bytes of K per instruction

@@ -317,7 +317,7 @@ bool plan_smem(RowsParams* p, int kv, int* smem_bytes) {
   p->epi_off = off; off += 2 * 128 * (int)sizeof(float);
   off = (off + 1023) & ~1023;
   p->w_off = off;
-  const int gk = p->kc == 2 ? 4 : p->kc == 4 ? kGK4 : 1;   // kernel offsets per stage (RowShape<KC>::GK)
+  const int gk = offsets_per_stage(p->kc);
   const int w_all = kv * p->w_bytes;
   const int avail = kSmemTotal - 1024 - off;
   // resident weights or one image per stage: whichever keeps more gathered offsets in flight; resident wins ties
