@@ -174,7 +174,7 @@ int sph_pack_weight(const void* d_weight, int dtype, int32_t kv, int32_t k_ch, i
 int sph_conv_uses_tensor_cores(int dtype, int32_t k_ch, int32_t n_ch);
 /* Which CUDA-core kernel runs when the tensor-core kernels do not take the combination (27 offsets assumed, operands
  * 16-byte aligned): 1 = the pair-compacting kernel for sparse levels (rows of 4 / 8 / 16 / 32 channels in and out, the
- * fp32 filter within its shared-memory budget), 0 = the row-walking kernel (any shape).  No reference counterpart. */
+ * fp32 filter within its shared-memory limit), 0 = the row-walking kernel (any shape).  No reference counterpart. */
 int sph_conv_uses_pair_kernel(int dtype, int32_t k_ch, int32_t n_ch);
 
 /* out[r,:] = epilogue( sum_k rows[ nbr[k][r], : ] @ weight[k] )   for r in [0, n_out)
