@@ -715,7 +715,7 @@ def main():
 TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per output row, 4-scan fp16 capture of these kernels, "
                   "scaled by the rows of the timed launches")
 TRAFFIC_BYTES_PER_OUT_ROW = {
-    "fp16": {"L0": 116.1, "L1": 140.8, "L2": 146.9, "L3": 210.1, "L4": 210.9, "L5": 292.1, "L6": 282.9, "L7": 285.9},
+    "fp16": {"L0": 116.2, "L1": 141.3, "L2": 146.5, "L3": 211.3, "L4": 208.9, "L5": 288.9, "L6": 280.6, "L7": 281.1},
 }
 
 if __name__ == "__main__":
