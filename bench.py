@@ -638,7 +638,8 @@ def main():
             "frac_tensor": round(t_f / t, 4), "frac_hbm": round(t_q / t, 4),
             "flops_per_launch": g["flops"] / g["launches"], "bytes_per_launch": g["bytes"] / g["launches"],
             "traffic": None if g["traffic"] is None else int(g["traffic"] / g["launches"]),
-            "traffic_source": None if g["traffic"] is None else TRAFFIC_SOURCE})
+            "traffic_source": None if g["traffic"] is None else TRAFFIC_SOURCE,
+            "busiest_unit_ncu": BUSIEST_UNIT.get(kernel)})
     by_kernel.sort(key=lambda r: -r["ms_per_step"])
     dom = by_kernel[0] if by_kernel else {}
     roofline = dict(dom)
@@ -714,6 +715,14 @@ def main():
 # so the write half undercounts.  A layer that is not listed has no captured figure (traffic: null).
 TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per output row, 4-scan fp16 capture of these kernels, "
                   "scaled by the rows of the timed launches")
+# What limits each instantiation according to the same capture (neither HBM nor the tensor pipe: the bench line's `bound`
+# is the roofline the work is reported against, this is the unit that was busiest).
+BUSIEST_UNIT = {
+    "conv_gather_rows_kernel<4,f16>": "shared-memory data pipe 92 % busy (gather writes 64 % + tensor-core operand reads 28 %); DRAM 12 %, tensor pipe 11 %",
+    "conv_gather_tc_kernel<8,f16>": "shared-memory data pipe 88 % busy (gather writes 58 % + operand reads 30 %); tensor pipe 47 %, DRAM 8 %",
+    "conv_gather_tc_kernel<2,f16>": "shared-memory data pipe 69-93 % busy (gather writes 52-72 % + operand reads 17-22 %); DRAM 9-13 %",
+    "conv_sparse_rows_kernel<4,16>": "instruction issue 68 % of the slots; DRAM 15 %",
+}
 TRAFFIC_BYTES_PER_OUT_ROW = {
     "fp16": {"L0": 116.2, "L1": 141.3, "L2": 146.5, "L3": 211.3, "L4": 208.9, "L5": 288.9, "L6": 280.6, "L7": 281.1},
 }
