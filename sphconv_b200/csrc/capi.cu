@@ -124,9 +124,9 @@ extern "C" int sph_conv_gather(const void* d_rows, int dtype, int64_t n_rows, co
                           relu, d_out, out_dtype, d_status, st);
   }
   SPH_CHECK_ARG(d_weight, "the CUDA-core kernels need the unpacked weight");
-  // narrow rows the tensor-core kernels do not take (the first layer of an encoder: 4 or 8 channels in, a sparse level)
-  // and small fp32 layers: the pair-compacting kernel (faster than the row-walking one from 1 to 22 neighbours per row)
-  if (conv_sparse_supported(dtype, kv, k_ch, n_ch) && out_dtype != SPH_I8 &&
+  // narrow rows the tensor-core kernels do not take (the first layer of an encoder: 4 or 8 channels in, a sparse level;
+  // int8 rows of up to 16 channels) and small fp32 layers: the pair-compacting kernel (faster than the row-walking one from 1 to 22 neighbours per row)
+  if (conv_sparse_supported(dtype, kv, k_ch, n_ch) &&
       ((((uintptr_t)d_rows | (uintptr_t)d_weight | (uintptr_t)d_out) & 15u) == 0)) {
     return conv_gather_sparse(d_rows, dtype, n_rows, d_weight, d_nbr, n_out, kv, k_ch, n_ch, flip_k, d_scale, d_bias,
                               relu, d_out, out_dtype, d_status, st);

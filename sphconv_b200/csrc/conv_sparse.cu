@@ -3,9 +3,9 @@
 // every (row, offset) slot of the table - as the tensor-core kernels do, 256 rows x all offsets per tile - spends its
 // time on slots that hold nothing.  Here the work is the PRESENT pairs:
 //
-//   * a CTA copies the filter [KV, iC, oC] into shared memory once, widened to fp32; its warps then take chunks of 32
-//     consecutive output rows.  A lane reads its row's table entries eight offsets at a time (one coalesced 128-byte
-//     load per offset), the next eight requested before the current ones are looked at;
+//   * a CTA copies the filter [KV, iC, oC] into shared memory once (as fp32, or as 16-bit values when it is large); its
+//     warps then take chunks of 32 consecutive output rows.  A lane reads its row's table entries eight offsets at a
+//     time (one coalesced 128-byte load per offset), the next eight requested before the current ones are looked at;
 //   * the warp walks the offsets and compacts the present entries into a list of (input row, output row in the chunk,
 //     weight index) with a ballot + prefix popcount;
 //   * whenever 32 items are listed, each lane fetches ONE item's input row (32 independent loads in flight per warp
@@ -50,12 +50,56 @@ template <> __device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(cons
   return __bfloat1622float2(*(const __nv_bfloat162*)p);
 }
 template <> __device__ __forceinline__ float2 pair_to_float2<float>(const float* p) { return *(const float2*)p; }
+template <> __device__ __forceinline__ float2 pair_to_float2<int8_t>(const int8_t* p) {
+  const char2 v = *(const char2*)p;
+  return make_float2((float)v.x, (float)v.y);
+}
+
+// Four consecutive filter weights as floats (the filter sits in shared memory as fp32, or as 16-bit values when it is large).
+template <typename W> __device__ __forceinline__ float4 quad_to_float4(const W* p);
+template <> __device__ __forceinline__ float4 quad_to_float4<float>(const float* p) { return *(const float4*)p; }
+template <> __device__ __forceinline__ float4 quad_to_float4<__half>(const __half* p) {
+  const uint2 raw = *(const uint2*)p;
+  const float2 a = __half22float2(*(const __half2*)&raw.x), b = __half22float2(*(const __half2*)&raw.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <> __device__ __forceinline__ float4 quad_to_float4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename W> __device__ __forceinline__ void store_pair(W* p, float2 v);
+template <> __device__ __forceinline__ void store_pair<float>(float* p, float2 v) { *(float2*)p = v; }
+template <> __device__ __forceinline__ void store_pair<__half>(__half* p, float2 v) { *(__half2*)p = __floats2half2_rn(v.x, v.y); }
+template <> __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16* p, float2 v) {
+  *(__nv_bfloat162*)p = __floats2bfloat162_rn(v.x, v.y);
+}
 
 // One input row (IC elements of T) -> IC floats in shared memory.
 template <typename T, int IC>
 __device__ __forceinline__ void stage_row(const T* __restrict__ src, float* __restrict__ dst) {
   constexpr int BYTES = IC * (int)sizeof(T);
-  if constexpr (BYTES == 8) {
+  if constexpr (sizeof(T) == 1) {
+    uint32_t raw[BYTES / 4];
+    if constexpr (BYTES == 4) {
+      raw[0] = __ldg((const uint32_t*)src);
+    } else if constexpr (BYTES == 8) {
+      const uint2 v = __ldg((const uint2*)src);
+      raw[0] = v.x; raw[1] = v.y;
+    } else {
+#pragma unroll
+      for (int q = 0; q < BYTES / 16; ++q) {
+        const uint4 v = __ldg((const uint4*)src + q);
+        raw[4 * q] = v.x; raw[4 * q + 1] = v.y; raw[4 * q + 2] = v.z; raw[4 * q + 3] = v.w;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < BYTES / 4; ++q) {
+      const uint32_t w = raw[q];
+      *(float4*)(dst + 4 * q) = make_float4((float)(int8_t)(w & 0xffu), (float)(int8_t)((w >> 8) & 0xffu),
+                                            (float)(int8_t)((w >> 16) & 0xffu), (float)(int8_t)(w >> 24));
+    }
+  } else if constexpr (BYTES == 8) {
     const uint2 raw = __ldg((const uint2*)src);
     const T* e = (const T*)&raw;
     const float2 a = pair_to_float2<T>(e), b = pair_to_float2<T>(e + 2);
@@ -83,6 +127,21 @@ __device__ __forceinline__ void store_group(void* out, int out_dtype, int64_t el
   if (out_dtype == SPH_F32) {
 #pragma unroll
     for (int j = 0; j < G; j += 4) *(float4*)((float*)out + elem + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else if (out_dtype == SPH_I8) {   // round to nearest, saturate at +-127
+    uint32_t w[G / 4];
+#pragma unroll
+    for (int j = 0; j < G; j += 4) {
+      uint32_t acc = 0;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int q = (int)fminf(fmaxf(rintf(v[j + t]), -127.f), 127.f);
+        acc |= ((uint32_t)q & 0xffu) << (8 * t);
+      }
+      w[j / 4] = acc;
+    }
+    uint8_t* dst = (uint8_t*)out + elem;
+    if constexpr (G == 8) *(uint2*)dst = make_uint2(w[0], w[1]);
+    else *(uint32_t*)dst = w[0];
   } else {
     uint32_t w[G / 2];
 #pragma unroll
@@ -104,12 +163,20 @@ __device__ __forceinline__ void store_group(void* out, int out_dtype, int64_t el
 constexpr int kSpGroup = 8;          // table offsets a lane looks at per step; the next step's are in flight meanwhile
 constexpr int kSpWPad = 16;          // floats between the filters of two offsets: neighbouring offsets on other banks
 
+// The filter in shared memory: fp32 when an offset has at most 256 weights (no conversions in the inner loop), else 16-bit
+// (the rows' own type; int8 weights as fp16, which holds them exactly) so that two CTAs still share a multiprocessor.
+template <typename T, bool Large> struct FilterType { using type = float; };
+template <> struct FilterType<__half, true> { using type = __half; };
+template <> struct FilterType<__nv_bfloat16, true> { using type = __nv_bfloat16; };
+template <> struct FilterType<int8_t, true> { using type = __half; };
+
 template <typename T, int IC, int OC> struct SparseShape {
+  using W = typename FilterType<T, (IC * OC > 256)>::type;
   static constexpr int XS = IC + 4;            // staged row stride in floats: 16-byte stores of 8 lanes hit 8 bank groups
   static constexpr int AS = OC + 4;            // accumulator row stride in floats
-  static constexpr int WS = IC * OC + kSpWPad; // filter stride of an offset in floats
+  static constexpr int WS = IC * OC + kSpWPad; // filter stride of an offset in elements
   static constexpr int WARP_BYTES = 32 * XS * 4 + 32 * AS * 4 + kSpList * 8;
-  static int smem_bytes(int kv) { return kv * WS * 4 + 2 * OC * 4 + kSpWarps * WARP_BYTES; }
+  static int smem_bytes(int kv) { return kv * WS * (int)sizeof(W) + 2 * OC * 4 + kSpWarps * WARP_BYTES; }
 };
 
 // Multiplies the first n listed items (n <= 32) of the warp into its accumulator tile.  `wb` is the warp's region of
@@ -117,8 +184,10 @@ template <typename T, int IC, int OC> struct SparseShape {
 // OC/4 lanes work on one item, four output channels each: a step of four input channels is one 16-byte read of the
 // staged row, four 16-byte reads of the filter and 16 FMAs.
 template <typename T, int IC, int OC>
-__device__ __noinline__ void sparse_flush(const T* __restrict__ rows, const float* sW, unsigned char* wb, int n) {
+__device__ __noinline__ void sparse_flush(const T* __restrict__ rows, const typename SparseShape<T, IC, OC>::W* sW,
+                                          unsigned char* wb, int n) {
   using S = SparseShape<T, IC, OC>;
+  using W = typename S::W;
   constexpr int LPI = OC / 4;                  // lanes per item
   constexpr int IPP = 32 / LPI;                // items per pass
   constexpr int XS = S::XS, AS = S::AS;
@@ -139,13 +208,13 @@ __device__ __noinline__ void sparse_flush(const T* __restrict__ rows, const floa
     const int rk = valid ? list_rk[it] : 0;
     const int r = rk & 31;
     const float* x = stage + (valid ? it : 0) * XS;
-    const float* w = sW + (rk >> 5) * S::WS + 4 * cl;
+    const W* w = sW + (rk >> 5) * S::WS + 4 * cl;
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < IC; j += 4) {
       const float4 xv = *(const float4*)(x + j);
-      const float4 w0 = *(const float4*)(w + (j + 0) * OC), w1 = *(const float4*)(w + (j + 1) * OC);
-      const float4 w2 = *(const float4*)(w + (j + 2) * OC), w3 = *(const float4*)(w + (j + 3) * OC);
+      const float4 w0 = quad_to_float4<W>(w + (j + 0) * OC), w1 = quad_to_float4<W>(w + (j + 1) * OC);
+      const float4 w2 = quad_to_float4<W>(w + (j + 2) * OC), w3 = quad_to_float4<W>(w + (j + 3) * OC);
       s.x = fmaf(xv.x, w0.x, s.x); s.y = fmaf(xv.x, w0.y, s.y); s.z = fmaf(xv.x, w0.z, s.z); s.w = fmaf(xv.x, w0.w, s.w);
       s.x = fmaf(xv.y, w1.x, s.x); s.y = fmaf(xv.y, w1.y, s.y); s.z = fmaf(xv.y, w1.z, s.z); s.w = fmaf(xv.y, w1.w, s.w);
       s.x = fmaf(xv.z, w2.x, s.x); s.y = fmaf(xv.z, w2.y, s.y); s.z = fmaf(xv.z, w2.z, s.z); s.w = fmaf(xv.z, w2.w, s.w);
@@ -175,8 +244,9 @@ __global__ void __launch_bounds__(kSpThreads, 4) conv_sparse_rows_kernel(SparseP
   constexpr int AS = S::AS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  float* sW = (float*)smem;                                      // [kv][WS]: the filter, widened to fp32
-  float* s_epi = sW + p.kv * S::WS;                              // scale[OC], bias[OC]
+  using W = typename S::W;
+  W* sW = (W*)smem;                                              // [kv][WS]: the filter
+  float* s_epi = (float*)(sW + p.kv * S::WS);                    // scale[OC], bias[OC]
   unsigned char* wb = (unsigned char*)(s_epi + 2 * OC) + warp * S::WARP_BYTES;
   float* acc = (float*)wb + 32 * S::XS;                          // [32][AS]
   int* list_i = (int*)(acc + 32 * AS);                           // [kSpList] input row
@@ -187,7 +257,7 @@ __global__ void __launch_bounds__(kSpThreads, 4) conv_sparse_rows_kernel(SparseP
     const int w_elems = p.kv * IC * OC;
     for (int e = threadIdx.x * 2; e < w_elems; e += kSpThreads * 2) {
       const int k = e / (IC * OC);
-      *(float2*)(sW + k * S::WS + (e - k * (IC * OC))) = pair_to_float2<T>(gw + e);
+      store_pair<W>(sW + k * S::WS + (e - k * (IC * OC)), pair_to_float2<T>(gw + e));
     }
   }
   for (int c = threadIdx.x; c < OC; c += kSpThreads) {
@@ -321,12 +391,15 @@ bool channels_ok(int c) { return c == 4 || c == 8 || c == 16 || c == 32; }
 
 }  // namespace
 
-// Shapes the kernel takes: fp32 / fp16 / bf16 rows of 4, 8, 16 or 32 channels in and out, the whole filter (plus the
-// warps' tiles) within 112 KB of shared memory so that at least two CTAs share a multiprocessor.
+// Shapes the kernel takes: fp32 / fp16 / bf16 / int8 rows of 4, 8, 16 or 32 channels in and out, the whole filter (plus
+// the warps' tiles) within 112 KB of shared memory so that at least two CTAs share a multiprocessor.  int8 products are
+// summed in fp32, which is exact while every partial sum stays below 2^24: KV * K * 127^2 must.
 bool conv_sparse_supported(int dtype, int kv, int K, int N) {
-  if (dtype != SPH_F32 && dtype != SPH_F16 && dtype != SPH_BF16) return false;
+  if (dtype != SPH_F32 && dtype != SPH_F16 && dtype != SPH_BF16 && dtype != SPH_I8) return false;
   if (!channels_ok(K) || !channels_ok(N)) return false;
-  const int64_t smem = (int64_t)kv * (K * N + kSpWPad) * 4 + 2 * N * 4 +
+  if (dtype == SPH_I8 && (int64_t)kv * K * 16129 >= (1 << 24)) return false;
+  const int w_size = (K * N > 256 && dtype != SPH_F32) ? 2 : 4;
+  const int64_t smem = (int64_t)kv * (K * N + kSpWPad) * w_size + 2 * N * 4 +
                        (int64_t)kSpWarps * (32 * (K + 4) * 4 + 32 * (N + 4) * 4 + kSpList * 8);
   return kv < (1 << 20) && smem <= 112 * 1024;
 }
@@ -334,7 +407,7 @@ bool conv_sparse_supported(int dtype, int kv, int K, int N) {
 int conv_gather_sparse(const void* rows, int dtype, int64_t n_rows, const void* weight, const int* nbr, int64_t n_out,
                        int kv, int K, int N, int flip_k, const float* scale, const float* bias, int relu, void* out,
                        int out_dtype, int* status, cudaStream_t st) {
-  if (!conv_sparse_supported(dtype, kv, K, N) || out_dtype == SPH_I8) {
+  if (!conv_sparse_supported(dtype, kv, K, N) || (out_dtype == SPH_I8 && dtype != SPH_I8)) {
     set_error("conv_gather_sparse: unsupported dtype/shape");
     return SPH_ERR_UNSUPPORTED;
   }
@@ -351,6 +424,7 @@ int conv_gather_sparse(const void* rows, int dtype, int64_t n_rows, const void* 
     case SPH_F32: return launch_sparse_ic<float>(p, K, N, st);
     case SPH_F16: return launch_sparse_ic<__half>(p, K, N, st);
     case SPH_BF16: return launch_sparse_ic<__nv_bfloat16>(p, K, N, st);
+    case SPH_I8: return launch_sparse_ic<int8_t>(p, K, N, st);
   }
   return SPH_ERR_UNSUPPORTED;
 }

@@ -65,7 +65,7 @@ class QuantEncoder:
         self.layers, self.in_scale, self.in_channels_padded = layers, in_scale, in_channels_padded
 
     def quantize_input(self, feature: torch.Tensor) -> torch.Tensor:
-        """float [n, C] -> int8 [n, C padded to 32] (zeros in the padding)."""
+        """float [n, C] -> int8 [n, C padded to the first layer's input width] (zeros in the padding)."""
         q = torch.round(feature.float() / self.in_scale).clamp_(-QMAX, QMAX).to(torch.int8)
         out = torch.zeros((q.shape[0], self.in_channels_padded), dtype=torch.int8, device=q.device)
         out[:, :q.shape[1]] = q
@@ -89,15 +89,26 @@ def quantize_encoder(net: Sequential, calib: SparseConvTensor) -> QuantEncoder:
     for m in convs:
         acts.append(_absmax_per_channel(x.feature))
         x = m(x)
-    # int8 rows must be at least 32 bytes for the tensor-core kernel (one kind::i8 instruction consumes 32 channels),
-    # so channel counts are padded to a multiple of 32 with zero weights: a padded output channel computes
-    # relu(0) = 0 and the next layer's padded input channels carry zero weights.
-    pad = lambda c: max(32, (c + 31) // 32 * 32)
+    # Channel counts at the layer boundaries.  The tensor-core kernel wants int8 rows of at least 32 bytes (one kind::i8
+    # instruction consumes 32 channels), so counts are padded to a multiple of 32 with zero weights: a padded output channel
+    # computes relu(0) = 0 and the next layer's padded input channels carry zero weights.  A layer with narrower rows keeps
+    # them (padded to 4, 8 or 16 only) where the pair-compacting CUDA-core kernel takes the pair of widths: the first,
+    # sparse levels then move a quarter of the bytes.
+    from . import _capi as C
+    lib = C.lib()
+    pad32 = lambda c: max(32, (c + 31) // 32 * 32)
+    narrow = lambda c: 4 if c <= 4 else 8 if c <= 8 else 16 if c <= 16 else pad32(c)
+    chans = [convs[0].in_channels] + [m.out_channels for m in convs]
+    width = [narrow(c) for c in chans]
+    width[-1] = chans[-1]                                             # the last layer's output is not padded
+    for li in range(len(convs) - 1, -1, -1):
+        if width[li] < 32 and not lib.sph_conv_uses_pair_kernel(C.SPH_I8, width[li], width[li + 1]):
+            width[li] = pad32(chans[li])
     layers = []
     for li, m in enumerate(convs):
         last = li == len(convs) - 1
         iC, oC = m.in_channels, m.out_channels
-        iP, oP = pad(iC), (oC if last else pad(oC))
+        iP, oP = width[li], width[li + 1]
         s_x = acts[li] / QMAX                                         # [iC]
         w = m.weight.detach().float().reshape(-1, iC, oC) * s_x.view(1, -1, 1)
         s_w = w.abs().amax(dim=(0, 1)).clamp_min(1e-12) / QMAX       # [oC]
@@ -111,4 +122,4 @@ def quantize_encoder(net: Sequential, calib: SparseConvTensor) -> QuantEncoder:
         bias_p[:oC] = bias / s_y
         layers.append(QuantConv(m, w_q.contiguous(), scale.contiguous(), bias_p.contiguous(), m.activation == 'relu',
                                 torch.float32 if last else torch.int8))
-    return QuantEncoder(layers, acts[0] / QMAX, pad(convs[0].in_channels))
+    return QuantEncoder(layers, acts[0] / QMAX, width[0])

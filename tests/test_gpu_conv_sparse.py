@@ -74,3 +74,24 @@ def test_dgrad_narrow_rows(iC, oC, dtype, subm):
     ref = conv_np.conv_dgrad(dout.double().cpu().numpy(), w.double().cpu().numpy(), pairs, n_in)
     _close(dfeat, ref, TOL[dtype])
     assert check_status() == 0
+
+
+@pytest.mark.parametrize("iC,oC", [(4, 16), (16, 16), (16, 32), (8, 8), (16, 4)])
+@pytest.mark.parametrize("subm,dens", [(True, 0.05), (True, 1.0), (False, 0.3)])
+def test_int8_narrow_rows_exact(iC, oC, subm, dens):
+    """int8 rows narrower than 32 bytes: products summed in fp32 (exact below 2^24), integer oracle, then the quantised
+    epilogue with int8 output."""
+    B, shape = 2, [9, 21, 13]
+    rng, feat, w, rules, rule_size, pairs, n_in, n_out = _setup(B, shape, subm, dens, 35, iC, oC, torch.int8)
+    out = ops.rule_conv(feat, w, rules, rule_size, n_out)
+    ref = conv_np.conv_forward(feat.cpu().numpy(), w.cpu().numpy(), pairs, n_out, dtype=np.int64)
+    assert out.dtype == torch.float32
+    assert (out.cpu().numpy().astype(np.int64) == ref).all()
+    scale = torch.as_tensor(rng.uniform(1e-4, 3e-4, size=oC), dtype=torch.float32, device=DEV)
+    bias = torch.as_tensor(rng.uniform(-20, 20, size=oC), dtype=torch.float32, device=DEV)
+    q = ops.rule_conv(feat, w, rules, rule_size, n_out, scale=scale, bias=bias, relu=True, out_dtype=torch.int8)
+    want = np.maximum(ref.astype(np.float32) * scale.cpu().numpy() + bias.cpu().numpy(), 0)
+    want = np.clip(np.rint(want), -127, 127).astype(np.int8)
+    diff = np.abs(q.cpu().numpy().astype(np.int32) - want.astype(np.int32))
+    assert q.dtype == torch.int8 and diff.max() <= 1 and (diff != 0).mean() < 1e-3   # ties at .5 may round differently
+    assert check_status() == 0
