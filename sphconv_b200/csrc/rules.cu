@@ -269,6 +269,8 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
 //     (batch, tile row, row), reads nbr[k][row] and ballot-compacts the hits into rules[tile][k].
 // Both do nothing when a column was found out of depth order; emit_rules_kernel then does the work.
 // ---------------------------------------------------------------------------------------------
+// KD_CT: the filter's depth extent when it is 3 (the depth loop is then unrolled), 0 = read it from the geometry.
+template <int KD_CT, bool HAS_T>
 __global__ void __launch_bounds__(256)
 nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, Geom g, int64_t in_nnz,
                 int64_t out_nnz, int* nbr, int* __restrict__ nbr_t, ColMask cm, int* __restrict__ status) {
@@ -304,7 +306,9 @@ nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, G
       }
       int cur_w = -1;
       uint2 e = make_uint2(0u, 0u);
-      for (int kd = 0; kd < g.KD; ++kd) {
+      const int KD = KD_CT ? KD_CT : g.KD;
+#pragma unroll
+      for (int kd = 0; kd < KD; ++kd) {
         const int iz = iz0 + kd * g.dD;
         int found = -1;
         if (col_ok && iz >= 0 && iz < g.D) {
@@ -317,7 +321,7 @@ nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, G
         }
         *dst = found;
         dst += out_nnz;
-        if (nbr_t) {
+        if (HAS_T) {
           if (found >= 0) dst_t[found] = (int)r;
           dst_t += in_nnz;
         }
@@ -919,8 +923,14 @@ int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int
   const bool fast = rows_parked && cm.table != nullptr && nbr != nullptr;
   if (fast) {
     if (out_nnz > 0) {
-      nbr_rows_kernel<<<(unsigned)div_up64(out_nnz, 256), 256, 0, st>>>(in_zp, out_zi, g, in_nnz, out_nnz, nbr, nbr_t,
-                                                                         cm, status);
+      const unsigned grid = (unsigned)div_up64(out_nnz, 256);
+#define SPH_NBR_ROWS(KD, T) nbr_rows_kernel<KD, T><<<grid, 256, 0, st>>>(in_zp, out_zi, g, in_nnz, out_nnz, nbr, nbr_t, cm, status)
+      if (g.KD == 3) {
+        if (nbr_t) SPH_NBR_ROWS(3, true); else SPH_NBR_ROWS(3, false);
+      } else {
+        if (nbr_t) SPH_NBR_ROWS(0, true); else SPH_NBR_ROWS(0, false);
+      }
+#undef SPH_NBR_ROWS
       SPH_LAUNCH_CHECK();
     }
     if (rule_size) {
