@@ -269,7 +269,7 @@ emit_rules_kernel(const int* __restrict__ in_zi, const int* __restrict__ in_zp, 
 //     (batch, tile row, row), reads nbr[k][row] and ballot-compacts the hits into rules[tile][k].
 // Both do nothing when a column was found out of depth order; emit_rules_kernel then does the work.
 // ---------------------------------------------------------------------------------------------
-// KD_CT: the filter's depth extent when it is 3 (the depth loop is then unrolled), 0 = read it from the geometry.
+// KD_CT = 3: the filter is 3 wide and 3 deep (those two loops are unrolled), 0 = extents read from the geometry.
 template <int KD_CT, bool HAS_T>
 __global__ void __launch_bounds__(256)
 nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, Geom g, int64_t in_nnz,
@@ -294,7 +294,9 @@ nbr_rows_kernel(const int* __restrict__ in_zp, const int* __restrict__ out_zi, G
   int* dst_t = nbr_t;
   for (int kh = 0; kh < g.KH; ++kh) {
     const int ix = ox * g.sH - g.pH + kh * g.dH;
-    for (int kw = 0; kw < g.KW; ++kw) {
+    const int KW = KD_CT ? KD_CT : g.KW;   // the unrolled form is the cubic 3 x 3 x 3 filter
+#pragma unroll
+    for (int kw = 0; kw < KW; ++kw) {
       const int iy = oy * g.sW - g.pW + kw * g.dW;
       const bool col_ok = ix >= 0 && ix < g.H && iy >= 0 && iy < g.W;
       int cstart = 0;
@@ -925,7 +927,7 @@ int launch_emit(const int* in_zi, const int* in_zp, const int* out_zi, const int
     if (out_nnz > 0) {
       const unsigned grid = (unsigned)div_up64(out_nnz, 256);
 #define SPH_NBR_ROWS(KD, T) nbr_rows_kernel<KD, T><<<grid, 256, 0, st>>>(in_zp, out_zi, g, in_nnz, out_nnz, nbr, nbr_t, cm, status)
-      if (g.KD == 3) {
+      if (g.KD == 3 && g.KW == 3) {
         if (nbr_t) SPH_NBR_ROWS(3, true); else SPH_NBR_ROWS(3, false);
       } else {
         if (nbr_t) SPH_NBR_ROWS(0, true); else SPH_NBR_ROWS(0, false);
