@@ -723,6 +723,26 @@ strided_bits_kernel(Geom g, int words_out, int64_t ncols_out, ColMask cm, uint32
           if (j < nw) u[j] |= __ldg(row + j).x;
       }
     }
+    if (g.sD == 2 && g.pD == 1 && g.KD == 3 && g.dD == 1) {
+      // The usual stride-2, 3-deep, padding-1 layer: output bin o looks at input bins 2o-1, 2o, 2o+1, i.e. at the even
+      // bits of x | x << 1 | x >> 1 over the 64 input bins [64w, 64w + 64) plus the last bin of the word before.
+      // w_lo is 2w - 1 (that word) for w > 0 and 0 for w = 0.
+      const int first = 2 * w - w_lo;                      // index of input word 2w in u[]
+      const uint32_t prev = first ? u[0] : 0u;
+      const uint32_t a = first ? u[1] : u[0], bw = first ? u[2] : u[1];
+      const uint32_t xa = a | (a << 1) | (a >> 1) | (prev >> 31);
+      const uint32_t xb = bw | (bw << 1) | (bw >> 1) | (a >> 31);
+      auto even_bits = [](uint32_t x) {                    // bits 0, 2, ..., 30 of x packed into bits 0 .. 15
+        x &= 0x55555555u;
+        x = (x | (x >> 1)) & 0x33333333u;
+        x = (x | (x >> 2)) & 0x0f0f0f0fu;
+        x = (x | (x >> 4)) & 0x00ff00ffu;
+        x = (x | (x >> 8)) & 0x0000ffffu;
+        return x;
+      };
+      out = even_bits(xa) | (even_bits(xb) << 16);
+      if (n_bits < 32) out &= (1u << n_bits) - 1u;
+    } else
     for (int bit = 0; bit < n_bits; ++bit) {
       const int base = (oz_lo + bit) * g.sD - g.pD;
       uint32_t hit = 0u;
