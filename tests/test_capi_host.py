@@ -78,3 +78,18 @@ def test_ops_refuse_cpu_tensors():
     zp = torch.zeros((1, 4, 4), dtype=torch.int32)
     with pytest.raises(RuntimeError, match="no CPU path"):
         ops.get_rules_subm(zi, zp, 1, [4, 4, 4], [4, 4, 4], [3, 3, 3], [1, 1, 1], [1, 1, 1], [1, 1, 1], [2, 2])
+
+
+def test_kernel_selection_predicates(lib):
+    """Which convolution kernel a shape gets (host-side answers; 27 offsets assumed)."""
+    tc, pair = lib.sph_conv_uses_tensor_cores, lib.sph_conv_uses_pair_kernel
+    # rows of 32 to 256 bytes: tensor cores, never the pair kernel
+    for dt, k, n in [(C.SPH_F16, 16, 16), (C.SPH_F16, 32, 32), (C.SPH_BF16, 64, 64), (C.SPH_I8, 32, 32), (C.SPH_I8, 64, 64)]:
+        assert tc(dt, k, n) == 1 and pair(dt, k, n) == 0
+    # narrower rows of 4 / 8 / 16 / 32 channels and small fp32 layers: the pair-compacting kernel
+    for dt, k, n in [(C.SPH_F16, 4, 16), (C.SPH_F16, 8, 8), (C.SPH_BF16, 4, 32), (C.SPH_F32, 16, 16), (C.SPH_F32, 4, 4),
+                     (C.SPH_I8, 4, 16), (C.SPH_I8, 16, 16), (C.SPH_I8, 16, 32)]:
+        assert tc(dt, k, n) == 0 and pair(dt, k, n) == 1
+    # odd channel counts and filters beyond its shared memory: the row-walking kernel
+    for dt, k, n in [(C.SPH_F16, 5, 16), (C.SPH_F32, 32, 32), (C.SPH_F32, 64, 64), (C.SPH_F16, 4, 64)]:
+        assert tc(dt, k, n) == 0 and pair(dt, k, n) == 0
