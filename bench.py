@@ -224,8 +224,10 @@ def kernel_of(lib, dcode, kind, k_ch, n_ch, esize, dtype_name):
     """Name of the kernel instantiation a conv / dgrad / wgrad layer launches (for grouping layers by kernel)."""
     tc = bool(lib.sph_conv_uses_tensor_cores(dcode, k_ch, n_ch))
     if kind == "wgrad":
-        tc = tc and dtype_name in ("fp16", "bf16")
-        return ("conv_wgrad_tc_kernel<%d>" % (k_ch * esize // 16)) if tc else "conv_wgrad_generic_kernel", tc
+        which = lib.sph_conv_wgrad_kernel(dcode, k_ch, n_ch)
+        if which == 1:
+            return "conv_wgrad_tc_kernel<%d>" % (k_ch * esize // 16), True
+        return ("conv_wgrad_pairs_kernel<%d,%d>" % (k_ch, n_ch)) if which == 2 else "conv_wgrad_generic_kernel", False
     if not tc:
         if lib.sph_conv_uses_pair_kernel(dcode, k_ch, n_ch):
             return "conv_sparse_rows_kernel<%d,%d>" % (k_ch, n_ch), tc

@@ -176,6 +176,10 @@ int sph_conv_uses_tensor_cores(int dtype, int32_t k_ch, int32_t n_ch);
  * 16-byte aligned): 1 = the pair-compacting kernel for sparse levels (rows of 4 / 8 / 16 / 32 channels in and out, the
  * fp32 filter within its shared-memory limit), 0 = the row-walking kernel (any shape).  No reference counterpart. */
 int sph_conv_uses_pair_kernel(int dtype, int32_t k_ch, int32_t n_ch);
+/* Which kernel sph_conv_wgrad runs for the combination (27 offsets assumed, operands 16-byte aligned): 1 = tcgen05,
+ * 2 = the pair-compacting CUDA-core kernel (narrow rows, small fp32 layers), 0 = the general CUDA-core kernel.
+ * No reference counterpart. */
+int sph_conv_wgrad_kernel(int dtype, int32_t k_ch, int32_t n_ch);
 
 /* out[r,:] = epilogue( sum_k rows[ nbr[k][r], : ] @ weight[k] )   for r in [0, n_out)
  * forward: ref rule_conv, src/sphconv/rule_conv.cu:286-336 (rows = feature, nbr = d_nbr, weight [KV,iC,oC]).

@@ -59,6 +59,7 @@ SIGNATURES = {
     "sph_pack_weight": (cint, [vp, cint, i32, i32, i32, vp, vp]),
     "sph_conv_uses_tensor_cores": (cint, [cint, i32, i32]),
     "sph_conv_uses_pair_kernel": (cint, [cint, i32, i32]),
+    "sph_conv_wgrad_kernel": (cint, [cint, i32, i32]),
     "sph_conv_gather": (cint, [vp, cint, i64, vp, vp, vp, i64, i32, i32, i32, cint, vp, vp, cint, vp, cint, vp, vp]),
     "sph_conv_wgrad": (cint, [vp, vp, cint, i64, vp, i64, i32, i32, i32, vp, cint, vp, vp]),
     "sph_init_tensor_scratch_bytes": (i64, [i32, c_i32p]),

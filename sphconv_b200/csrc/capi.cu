@@ -63,6 +63,10 @@ int conv_gather_sparse(const void* rows, int dtype, int64_t n_rows, const void* 
                        int kv, int K, int N, int flip_k, const float* scale, const float* bias, int relu, void* out,
                        int out_dtype, int* status, cudaStream_t st);
 
+bool conv_wgrad_pairs_supported(int dtype, int kv, int K, int N);
+int conv_wgrad_pairs(const void* rows, const void* dout, int dtype, int64_t n_rows, const int* nbr, int64_t n_out,
+                     int kv, int K, int N, float* dw, int* status, cudaStream_t st);
+
 // conv_wgrad_tc.cu
 bool conv_wgrad_tc_supported(int dtype, int kv, int K, int N);
 int conv_wgrad_tc(const void* rows, const void* dout, int dtype, int64_t n_rows, const int* nbr, int64_t n_out, int kv,
@@ -93,6 +97,11 @@ extern "C" int sph_conv_uses_tensor_cores(int dtype, int32_t k_ch, int32_t n_ch)
 
 extern "C" int sph_conv_uses_pair_kernel(int dtype, int32_t k_ch, int32_t n_ch) {
   return (!conv_tc_supported(dtype, 27, k_ch, n_ch) && conv_sparse_supported(dtype, 27, k_ch, n_ch)) ? 1 : 0;
+}
+
+extern "C" int sph_conv_wgrad_kernel(int dtype, int32_t k_ch, int32_t n_ch) {
+  if (conv_wgrad_tc_supported(dtype, 27, k_ch, n_ch)) return 1;
+  return conv_wgrad_pairs_supported(dtype, 27, k_ch, n_ch) ? 2 : 0;
 }
 
 static bool out_dtype_ok(int dtype, int out_dtype) {
@@ -146,5 +155,8 @@ extern "C" int sph_conv_wgrad(const void* d_rows, const void* d_dout, int dtype,
   SPH_CHECK_ARG(d_rows && d_dout && d_nbr, "null pointer");
   if (conv_wgrad_tc_supported(dtype, kv, k_ch, n_ch))
     return conv_wgrad_tc(d_rows, d_dout, dtype, n_rows, d_nbr, n_out, kv, k_ch, n_ch, d_dweight, d_status, st);
+  // narrow rows the tensor-core kernel does not take and small fp32 layers: the pair-compacting walk
+  if (conv_wgrad_pairs_supported(dtype, kv, k_ch, n_ch) && ((((uintptr_t)d_rows | (uintptr_t)d_dout) & 15u) == 0))
+    return conv_wgrad_pairs(d_rows, d_dout, dtype, n_rows, d_nbr, n_out, kv, k_ch, n_ch, d_dweight, d_status, st);
   return conv_wgrad_generic(d_rows, d_dout, dtype, n_rows, d_nbr, n_out, kv, k_ch, n_ch, d_dweight, d_status, st);
 }

@@ -389,6 +389,194 @@ int launch_sparse_ic(const SparseParams& p, int K, int N, cudaStream_t st) {
 
 bool channels_ok(int c) { return c == 4 || c == 8 || c == 16 || c == 32; }
 
+// ---- weight gradient of the same narrow, sparse layers --------------------------------------------------------------
+//   dW[k] += x[i,:]^T dY[o,:]   over the present pairs (i, o) of offset k
+// Same walk as the forward kernel: a warp takes 32 consecutive output rows, stages their dY rows once, lists the present
+// (input row, row in the chunk, offset) items offset by offset, fetches 32 input rows at a time and then goes through the
+// items one after the other with the lanes spread over the iC x oC elements of the product.  The list is offset-major,
+// so a lane's running sums belong to one offset at a time and are added to the CTA's copy of dW (shared memory) when the
+// offset changes; the CTA adds its copy to the fp32 gradient in global memory once, at the end.
+struct WgradParams {
+  const void* rows;                  // [n_rows, IC]
+  const void* dout;                  // [n_out, OC]
+  const int* nbr;                    // [KV, n_out]
+  int64_t n_rows, n_out, n_chunks;
+  int kv;
+  float* dw;                         // [KV, IC, OC], accumulated into
+  int* status;
+};
+
+template <int IC, int OC> struct WgradShape {
+  static constexpr int E = IC * OC;                      // elements of one offset's gradient
+  static constexpr int EPL = (E + 31) / 32;              // elements per lane
+  static constexpr int XS = IC + 4, DS = OC + 4;         // staged row strides in floats
+  static constexpr int WARP_BYTES = 32 * XS * 4 + 32 * DS * 4 + kSpList * 8;
+  static int smem_bytes(int kv) { return kv * E * 4 + kSpWarps * WARP_BYTES; }
+};
+
+template <typename T, int IC, int OC>
+__global__ void __launch_bounds__(kSpThreads, 3) conv_wgrad_pairs_kernel(WgradParams p) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  using S = WgradShape<IC, OC>;
+  constexpr int E = S::E, EPL = S::EPL, XS = S::XS, DS = S::DS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* s_dw = (float*)smem;                                    // [kv][E]
+  unsigned char* wb = (unsigned char*)(s_dw + p.kv * E) + warp * S::WARP_BYTES;
+  float* stage = (float*)wb;                                     // [32][XS]: input rows of the listed items
+  float* dys = stage + 32 * XS;                                  // [32][DS]: dY rows of the chunk
+  int* list_i = (int*)(dys + 32 * DS);
+  int* list_rk = list_i + kSpList;
+
+  for (int e = threadIdx.x; e < p.kv * E; e += kSpThreads) s_dw[e] = 0.f;
+  __syncthreads();
+
+  const T* rows = (const T*)p.rows;
+  const T* dout = (const T*)p.dout;
+  const unsigned lane_lt = (1u << lane) - 1u;
+  int ic_of[EPL], oc_of[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    const int e = lane + 32 * j;
+    ic_of[j] = (e / OC) % IC;                                    // lanes beyond E (E < 32) repeat an element and skip the add
+    oc_of[j] = e % OC;
+  }
+  float acc[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) acc[j] = 0.f;
+  int cur_k = 0;
+
+  // Adds the running sums to the CTA's gradient of offset cur_k.
+  auto spill = [&]() {
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E && acc[j] != 0.f) atomicAdd(s_dw + cur_k * E + e, acc[j]);
+      acc[j] = 0.f;
+    }
+  };
+  // The first n listed items: fetch their input rows, then one item after the other.
+  auto flush = [&](int n) {
+    if (lane < n) stage_row<T, IC>(rows + (int64_t)list_i[lane] * IC, stage + lane * XS);
+    __syncwarp();
+    for (int it = 0; it < n; ++it) {
+      const int rk = list_rk[it];
+      const int k = rk >> 5;
+      if (k != cur_k) {                                          // uniform: the list is offset-major
+        spill();
+        cur_k = k;
+      }
+      const float* x = stage + it * XS;
+      const float* d = dys + (rk & 31) * DS;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) acc[j] = fmaf(x[ic_of[j]], d[oc_of[j]], acc[j]);
+    }
+    __syncwarp();
+  };
+
+  const int64_t warps_total = (int64_t)gridDim.x * kSpWarps;
+  for (int64_t ch = (int64_t)blockIdx.x * kSpWarps + warp; ch < p.n_chunks; ch += warps_total) {
+    const int64_t o = ch * 32 + lane;
+    const bool row_ok = o < p.n_out;
+    const int* col = p.nbr + o;
+    __syncwarp();                                                // the previous chunk's items are done with dys
+    if (row_ok) stage_row<T, OC>(dout + o * OC, dys + lane * DS);
+    int cnt = 0;
+    int ahead[kSpGroup];
+#pragma unroll
+    for (int u = 0; u < kSpGroup; ++u) ahead[u] = (row_ok && u < p.kv) ? __ldg(col + (int64_t)u * p.n_out) : -1;
+    __syncwarp();
+#pragma unroll 1
+    for (int k0 = 0; k0 < p.kv; k0 += kSpGroup) {
+      int v[kSpGroup];
+#pragma unroll
+      for (int u = 0; u < kSpGroup; ++u) {
+        v[u] = ahead[u];
+        const int kk = k0 + kSpGroup + u;
+        ahead[u] = (row_ok && kk < p.kv) ? __ldg(col + (int64_t)kk * p.n_out) : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < kSpGroup; ++u) {
+        int i = v[u];
+        if (i >= p.n_rows) {
+          if (p.status) atomicOr(p.status, SPH_STATUS_BAD_INDEX);
+          i = -1;
+        }
+        const unsigned m = __ballot_sync(0xffffffffu, i >= 0);
+        if (m == 0u) continue;
+        if (i >= 0) {
+          const int pos = cnt + __popc(m & lane_lt);
+          list_i[pos] = i;
+          list_rk[pos] = lane | ((k0 + u) << 5);
+        }
+        cnt += __popc(m);
+        if (cnt >= 32) {
+          __syncwarp();
+          flush(32);
+          const int rem = cnt - 32;
+          int ti = 0, trk = 0;
+          if (lane < rem) { ti = list_i[32 + lane]; trk = list_rk[32 + lane]; }
+          __syncwarp();
+          if (lane < rem) { list_i[lane] = ti; list_rk[lane] = trk; }
+          cnt = rem;
+        }
+      }
+    }
+    if (cnt) {
+      __syncwarp();
+      flush(cnt);
+    }
+  }
+  spill();
+  __syncthreads();
+  for (int e = threadIdx.x; e < p.kv * E; e += kSpThreads) {
+    const float v = s_dw[e];
+    if (v != 0.f) atomicAdd(p.dw + e, v);
+  }
+}
+
+template <typename T, int IC, int OC>
+int launch_wgrad_pairs(const WgradParams& p, cudaStream_t st) {
+  using S = WgradShape<IC, OC>;
+  const int smem = S::smem_bytes(p.kv);
+  auto kern = conv_wgrad_pairs_kernel<T, IC, OC>;
+  if (smem > 48 * 1024) SPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int per_sm = 0;
+  SPH_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kSpThreads, smem));
+  const int sms = current_sm_count();
+  if (sms <= 0 || per_sm <= 0) {
+    set_error("conv_wgrad_pairs: the kernel does not fit on a multiprocessor");
+    return SPH_ERR_CUDA;
+  }
+  const int64_t want = div_up64(p.n_chunks, kSpWarps);
+  const int64_t grid = want < (int64_t)sms * per_sm ? want : (int64_t)sms * per_sm;
+  kern<<<(unsigned)grid, kSpThreads, smem, st>>>(p);
+  SPH_LAUNCH_CHECK();
+  return SPH_OK;
+}
+
+template <typename T, int IC>
+int launch_wgrad_pairs_oc(const WgradParams& p, int N, cudaStream_t st) {
+  switch (N) {
+    case 4: return launch_wgrad_pairs<T, IC, 4>(p, st);
+    case 8: return launch_wgrad_pairs<T, IC, 8>(p, st);
+    case 16: return launch_wgrad_pairs<T, IC, 16>(p, st);
+    case 32: return launch_wgrad_pairs<T, IC, 32>(p, st);
+  }
+  return SPH_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+int launch_wgrad_pairs_ic(const WgradParams& p, int K, int N, cudaStream_t st) {
+  switch (K) {
+    case 4: return launch_wgrad_pairs_oc<T, 4>(p, N, st);
+    case 8: return launch_wgrad_pairs_oc<T, 8>(p, N, st);
+    case 16: return launch_wgrad_pairs_oc<T, 16>(p, N, st);
+    case 32: return launch_wgrad_pairs_oc<T, 32>(p, N, st);
+  }
+  return SPH_ERR_UNSUPPORTED;
+}
+
+
 }  // namespace
 
 // Shapes the kernel takes: fp32 / fp16 / bf16 / int8 rows of 4, 8, 16 or 32 channels in and out, the whole filter (plus
@@ -425,6 +613,37 @@ int conv_gather_sparse(const void* rows, int dtype, int64_t n_rows, const void* 
     case SPH_F16: return launch_sparse_ic<__half>(p, K, N, st);
     case SPH_BF16: return launch_sparse_ic<__nv_bfloat16>(p, K, N, st);
     case SPH_I8: return launch_sparse_ic<int8_t>(p, K, N, st);
+  }
+  return SPH_ERR_UNSUPPORTED;
+}
+
+// Weight gradient by the pair-compacting walk: fp32 / fp16 / bf16 rows of 4, 8, 16 or 32 channels on both sides, at
+// most 512 elements per offset, the CTA's copy of the gradient plus the warps' tiles within 120 KB of shared memory.
+bool conv_wgrad_pairs_supported(int dtype, int kv, int K, int N) {
+  if (dtype != SPH_F32 && dtype != SPH_F16 && dtype != SPH_BF16) return false;
+  if (!channels_ok(K) || !channels_ok(N) || K * N > 512) return false;
+  const int64_t smem = (int64_t)kv * K * N * 4 + (int64_t)kSpWarps * (32 * (K + 4) * 4 + 32 * (N + 4) * 4 + kSpList * 8);
+  return kv < (1 << 20) && smem <= 120 * 1024;
+}
+
+int conv_wgrad_pairs(const void* rows, const void* dout, int dtype, int64_t n_rows, const int* nbr, int64_t n_out,
+                     int kv, int K, int N, float* dw, int* status, cudaStream_t st) {
+  if (!conv_wgrad_pairs_supported(dtype, kv, K, N)) {
+    set_error("conv_wgrad_pairs: unsupported dtype/shape");
+    return SPH_ERR_UNSUPPORTED;
+  }
+  if (((uintptr_t)rows | (uintptr_t)dout) & 15u) {
+    set_error("conv_wgrad_pairs: rows and dout must be 16-byte aligned");
+    return SPH_ERR_INVALID;
+  }
+  WgradParams p;
+  p.rows = rows; p.dout = dout; p.nbr = nbr;
+  p.n_rows = n_rows; p.n_out = n_out; p.n_chunks = div_up64(n_out, 32);
+  p.kv = kv; p.dw = dw; p.status = status;
+  switch (dtype) {
+    case SPH_F32: return launch_wgrad_pairs_ic<float>(p, K, N, st);
+    case SPH_F16: return launch_wgrad_pairs_ic<__half>(p, K, N, st);
+    case SPH_BF16: return launch_wgrad_pairs_ic<__nv_bfloat16>(p, K, N, st);
   }
   return SPH_ERR_UNSUPPORTED;
 }

@@ -93,3 +93,8 @@ def test_kernel_selection_predicates(lib):
     # odd channel counts and filters beyond its shared memory: the row-walking kernel
     for dt, k, n in [(C.SPH_F16, 5, 16), (C.SPH_F32, 32, 32), (C.SPH_F32, 64, 64), (C.SPH_F16, 4, 64)]:
         assert tc(dt, k, n) == 0 and pair(dt, k, n) == 0
+    # weight gradient: 1 = tensor cores, 2 = the pair-compacting walk, 0 = the general CUDA-core kernel
+    wk = lib.sph_conv_wgrad_kernel
+    assert wk(C.SPH_BF16, 32, 32) == 1 and wk(C.SPH_F16, 16, 16) == 1 and wk(C.SPH_F16, 64, 64) == 1
+    assert wk(C.SPH_BF16, 4, 16) == 2 and wk(C.SPH_F32, 16, 16) == 2 and wk(C.SPH_F32, 16, 32) == 2
+    assert wk(C.SPH_F32, 64, 64) == 0 and wk(C.SPH_F16, 5, 16) == 0 and wk(C.SPH_I8, 16, 16) == 0

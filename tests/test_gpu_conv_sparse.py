@@ -95,3 +95,23 @@ def test_int8_narrow_rows_exact(iC, oC, subm, dens):
     diff = np.abs(q.cpu().numpy().astype(np.int32) - want.astype(np.int32))
     assert q.dtype == torch.int8 and diff.max() <= 1 and (diff != 0).mean() < 1e-3   # ties at .5 may round differently
     assert check_status() == 0
+
+
+@pytest.mark.parametrize("iC,oC", [(4, 16), (16, 4), (8, 8), (4, 4), (16, 32), (32, 16)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("subm,dens,ks", [(True, 0.05, (3, 3, 3)), (True, 1.0, (3, 3, 3)), (False, 0.3, (3, 3, 3)),
+                                          (True, 0.4, (5, 3, 3))])
+def test_wgrad_narrow_rows(iC, oC, dtype, subm, dens, ks):
+    """Weight gradient of the narrow layers (the pair-compacting walk where the tensor-core kernel does not take the
+    shape; 16x32 / 32x16 take it in fp32 only) against the float64 oracle, fp32 accumulation checked in place."""
+    B, shape = 2, [9, 17, 13]
+    rng, feat, w, rules, rule_size, pairs, n_in, n_out = _setup(B, shape, subm, dens, 36, iC, oC, dtype, ks=ks)
+    dout = torch.as_tensor(rng.standard_normal((n_out, oC)), dtype=torch.float32, device=DEV).to(dtype)
+    kv = w.shape[0]
+    buf = torch.full((kv, iC, oC), 0.5, dtype=torch.float32, device=DEV)
+    ops.rule_conv_d_weight(feat, dout, rules, rule_size, out=buf, accumulate=True)      # adds to what the buffer holds
+    ref = conv_np.conv_wgrad(feat.double().cpu().numpy(), dout.double().cpu().numpy(), pairs, kv)
+    got = buf.double().cpu().numpy() - 0.5
+    scale = max(np.abs(ref).max(), 1.0)
+    assert np.abs(got - ref).max() <= TOL[dtype] * scale
+    assert check_status() == 0
