@@ -283,3 +283,19 @@ def test_deep_grid(subm):
     res = oracle_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
     assert_rules_equal(res, oz_idx, oz_ptr.reshape(res["oz_ptr"].shape), rules, rule_size)
     assert_tables_match(res, rules, z_idx.shape[0], oz_idx.shape[0])
+
+
+@pytest.mark.parametrize("depth", [3, 5, 31, 32, 33, 63, 64, 65, 66, 100, 129, 256])
+@pytest.mark.parametrize("dens", [0.15, 1.0])
+def test_stride2_depth_pattern_word_boundaries(depth, dens):
+    """The usual stride-2, 3-deep, padding-1 layer at depths around the 32-bin word boundaries of the column index: the
+    output pattern (oz_idx, oz_ptr), the pair lists and the tables against the oracle, sparse and completely full."""
+    B, shape, tile = 2, [5, 6, depth], [2, 2]
+    rng = np.random.default_rng(900 + depth)
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, dens)
+    ks, st, pd = [3, 3, 3], [2, 2, 2], [1, 1, 1]
+    zi, zp, osh, oz_idx, oz_ptr, rules, rule_size = gpu_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, False)
+    res = oracle_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, False)
+    assert_rules_equal(res, oz_idx, oz_ptr, rules, rule_size)
+    assert_tables_match(res, rules, z_idx.shape[0], oz_idx.shape[0])
+    assert check_status() & 1 == 0
