@@ -299,3 +299,21 @@ def test_stride2_depth_pattern_word_boundaries(depth, dens):
     assert_rules_equal(res, oz_idx, oz_ptr, rules, rule_size)
     assert_tables_match(res, rules, z_idx.shape[0], oz_idx.shape[0])
     assert check_status() & 1 == 0
+
+
+@pytest.mark.parametrize("subm", [True, False])
+def test_more_runs_per_tile_than_one_staging_pass(subm):
+    """150 scans in the batch: a tile of 2 x 2 columns then has 300 (batch, tile row) runs, more than the pair-list kernels
+    stage at a time (128), so they go through a tile in several passes."""
+    B, shape, tile = 150, [4, 6, 9], [2, 2]
+    rng = np.random.default_rng(77)
+    z_idx, z_ptr = synthetic.make_random_occupancy(rng, B, shape, 0.4)
+    ks = [3, 3, 3]
+    st, pd = ([1, 1, 1], [1, 1, 1]) if subm else ([2, 2, 2], [1, 1, 1])
+    zi, zp, osh, oz_idx, oz_ptr, rules, rule_size = gpu_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    res = oracle_rules(z_idx, z_ptr, B, shape, ks, st, pd, tile, subm)
+    if subm:
+        oz_ptr = oz_ptr.reshape(B, *shape[:2])
+    assert_rules_equal(res, oz_idx, oz_ptr, rules, rule_size)
+    assert_tables_match(res, rules, z_idx.shape[0], oz_idx.shape[0])
+    assert check_status() & 1 == 0
