@@ -815,17 +815,20 @@ scan_columns_kernel(int* __restrict__ counts, int64_t ncols, const int* __restri
 __global__ void __launch_bounds__(kScanThreads)
 write_oz_idx_kernel(const uint32_t* __restrict__ mask, const int* __restrict__ oz_ptr, int words, int64_t ncols,
                     int* __restrict__ oz_idx, int* __restrict__ row_col) {
-  const int64_t c = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
-  if (c >= ncols) return;
+  // one thread per (column, 32-bin word): its first row is the column's start plus the bins of the words before it
+  const int64_t t = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
+  if (t >= ncols * words) return;
+  const int64_t c = t / words;
+  const int w = (int)(t - c * words);
+  uint32_t m = mask[t];
+  if (m == 0u) return;
   int pos = c == 0 ? 0 : oz_ptr[c - 1];
-  for (int w = 0; w < words; ++w) {
-    uint32_t m = mask[c * words + w];
-    while (m) {
-      int bit = __ffs(m) - 1;
-      if (row_col) row_col[pos] = (int)c;   // column id of the row, for nbr_rows_kernel
-      oz_idx[pos++] = w * 32 + bit;
-      m &= m - 1;
-    }
+  for (int j = 0; j < w; ++j) pos += __popc(mask[c * words + j]);
+  while (m) {
+    const int bit = __ffs(m) - 1;
+    if (row_col) row_col[pos] = (int)c;   // column id of the row, for nbr_rows_kernel
+    oz_idx[pos++] = w * 32 + bit;
+    m &= m - 1;
   }
 }
 
@@ -1314,8 +1317,8 @@ extern "C" int sph_rules_strided_fill(const int32_t* d_z_idx, const int32_t* d_z
   StridedScratch l = strided_layout(g, nnz);
   const uint32_t* mask = (const uint32_t*)d_scratch;
   if (out_nnz > 0) {
-    write_oz_idx_kernel<<<l.nblk, kScanThreads, 0, st>>>(mask, d_oz_ptr, l.words, l.ncols, d_oz_idx,
-                                                         parked_columns(g, d_nbr, out_nnz));
+    write_oz_idx_kernel<<<(unsigned)div_up64(l.ncols * l.words, kScanThreads), kScanThreads, 0, st>>>(
+        mask, d_oz_ptr, l.words, l.ncols, d_oz_idx, parked_columns(g, d_nbr, out_nnz));
     SPH_LAUNCH_CHECK();
   }
   return launch_emit(d_z_idx, d_z_ptr, d_oz_idx, d_oz_ptr, g, nnz, out_nnz, tile_n_max, d_rules, d_rule_size,
