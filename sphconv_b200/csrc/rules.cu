@@ -92,6 +92,49 @@ build_colmask_kernel(const int* __restrict__ zi, const int* __restrict__ zp, int
   table[t] = make_uint2(bits, (uint32_t)below);
 }
 
+// The same index with one thread per COLUMN for columns of up to 8 words (depth <= 256): the column's rows are read
+// once, the words are built in registers and written with 16-byte stores (one thread per column and word reads the rows
+// of the column WORDS times).
+template <int WORDS>
+__global__ void __launch_bounds__(256)
+build_colmask_cols_kernel(const int* __restrict__ zi, const int* __restrict__ zp, int64_t ncols, int D,
+                          uint2* __restrict__ table, int* __restrict__ unsorted, int* __restrict__ row_col) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ncols) return;
+  const int s = col_start(zp, c), e = __ldg(zp + c);
+  uint32_t bits[WORDS];
+#pragma unroll
+  for (int w = 0; w < WORDS; ++w) bits[w] = 0u;
+  int prev = -1;
+  bool bad = false;
+  for (int r = s; r < e; ++r) {
+    const int z = __ldg(zi + r);
+    if (z <= prev || z >= D) bad = true;
+    prev = z;
+    if (row_col) row_col[r] = (int)c;
+    if (z >= 0 && z < D) {
+      const int zw = z >> 5;
+      const uint32_t bit = 1u << (z & 31);
+#pragma unroll
+      for (int w = 0; w < WORDS; ++w)
+        if (zw == w) bits[w] |= bit;
+    }
+  }
+  if (bad) *unsorted = 1;
+  uint32_t below = 0u;
+  uint2* dst = table + c * WORDS;
+  if constexpr (WORDS == 1) {
+    dst[0] = make_uint2(bits[0], 0u);
+  } else {
+#pragma unroll
+    for (int w = 0; w < WORDS; w += 2) {
+      const uint32_t b1 = below + (uint32_t)__popc(bits[w]);
+      *(uint4*)(dst + w) = make_uint4(bits[w], below, bits[w + 1], b1);
+      below = b1 + (uint32_t)__popc(bits[w + 1]);
+    }
+  }
+}
+
 // One CTA per output tile.  in_* describe the input tensor, out_* the output tensor (the same
 // arrays for a submanifold layer).
 __global__ void __launch_bounds__(kEmitThreads)
@@ -883,9 +926,17 @@ int build_colmask(const int* zi, const int* zp, const Geom& g, int64_t in_nnz, v
   cm->unsorted = (const int*)scratch;
   cm->words = words;
   cm->table = (const uint2*)((char*)scratch + 256);
-  build_colmask_kernel<<<(unsigned)div_up64(ncols * words, 256), 256, 0, st>>>(zi, zp, ncols, words, g.D,
-                                                                        (uint2*)((char*)scratch + 256), (int*)scratch,
-                                                                        row_col);
+  uint2* table = (uint2*)((char*)scratch + 256);
+  const unsigned col_grid = (unsigned)div_up64(ncols, 256);
+  switch (words) {
+    case 1: build_colmask_cols_kernel<1><<<col_grid, 256, 0, st>>>(zi, zp, ncols, g.D, table, (int*)scratch, row_col); break;
+    case 2: build_colmask_cols_kernel<2><<<col_grid, 256, 0, st>>>(zi, zp, ncols, g.D, table, (int*)scratch, row_col); break;
+    case 4: build_colmask_cols_kernel<4><<<col_grid, 256, 0, st>>>(zi, zp, ncols, g.D, table, (int*)scratch, row_col); break;
+    case 8: build_colmask_cols_kernel<8><<<col_grid, 256, 0, st>>>(zi, zp, ncols, g.D, table, (int*)scratch, row_col); break;
+    default:
+      build_colmask_kernel<<<(unsigned)div_up64(ncols * words, 256), 256, 0, st>>>(zi, zp, ncols, words, g.D, table,
+                                                                            (int*)scratch, row_col);
+  }
   SPH_LAUNCH_CHECK();
   return SPH_OK;
 }
