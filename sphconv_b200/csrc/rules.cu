@@ -928,7 +928,9 @@ int build_colmask(const int* zi, const int* zp, const Geom& g, int64_t in_nnz, v
   cm->table = (const uint2*)((char*)scratch + 256);
   uint2* table = (uint2*)((char*)scratch + 256);
   const unsigned col_grid = (unsigned)div_up64(ncols, 256);
-  switch (words) {
+  // one thread per column pays off on large grids; a small grid (a few hundred CTAs of the other form) is launch-bound
+  // either way and has more threads in flight with one thread per column and word
+  switch (ncols >= 100000 ? words : 0) {
     case 1: build_colmask_cols_kernel<1><<<col_grid, 256, 0, st>>>(zi, zp, ncols, g.D, table, (int*)scratch, row_col); break;
     case 2: build_colmask_cols_kernel<2><<<col_grid, 256, 0, st>>>(zi, zp, ncols, g.D, table, (int*)scratch, row_col); break;
     case 4: build_colmask_cols_kernel<4><<<col_grid, 256, 0, st>>>(zi, zp, ncols, g.D, table, (int*)scratch, row_col); break;
